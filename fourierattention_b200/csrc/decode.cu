@@ -1,0 +1,1034 @@
+// Decode attention over the Fourier-compressed KV cache (one query token per sequence).
+//
+// Scores and outputs of the compressed dims are never rebuilt per token.  With
+//   w[h,n] = sum_m C_k[n,m] scale_k[m] q_c[h,m]           (a mat-vec over the coefficients)
+// the score of middle-span token l is (1/N) sum_n [w_cos[n] cos(2 pi l n/T) + w_sin[n] sin(..)]
+// + const + q_n . k_verbatim[l], and with g[h,n] = sum_l p[l] cos/sin(2 pi l n/T) the compressed
+// V dims of the output are scale_v*((1/N) C_v^T g - avg_vd*P) + avg_vu*P.  The basis of a tile of
+// J consecutive tokens is a fixed J x N table times a per-frequency rotation, so the table lives in
+// shared memory for the whole kernel and only w (forward) and g (backward) are rotated per tile.
+//
+// Four launches per call:
+//   prepare  : w and const from q and C_k                      (reads C_k once)
+//   main     : split-KV pass over sinks+window rows and over the middle span; per chunk partials
+//              (max, denominator, verbatim-V numerator, g)      (reads every cache row once)
+//   contract : merge g over chunks, contract with C_v           (reads C_v once)
+//   output   : merge numerators/denominators, add the compressed-V part, normalise
+#include <math.h>
+
+#include "common.cuh"
+
+namespace fa {
+
+constexpr int R_MAX = 8;        // query heads per KV head
+constexpr int DEC_THREADS = 256;
+constexpr int IT_G = 4;         // (frequency, 8-head block) items per thread in the g update
+constexpr int IT_V = 4;         // verbatim-V columns per thread
+constexpr int IT_IL = 2;        // 4-dim groups per thread in the sinks+window PV
+constexpr float NEG_BIG = -1.0e30f;
+
+struct DecodeParams {
+  fa_decode_args_t a;
+  int R, F, n_il;
+  float c2;  // sm_scale * log2(e)
+  // plan
+  int J, kvh, HG, HGp, n_groups, TR, Hqp;
+  int il_chunk_rows, n_il_chunks, mid_chunk, n_mid_chunks, NCH;
+  int n_rb, rb_rows;
+  int pitchK, pitchV, qpitch;
+  int smem_main, smem_prepare, smem_contract;
+  // scratch
+  float *w, *cst, *m_part, *l_part, *o_part, *g_part, *cv_part;
+  int64_t scratch_floats;
+};
+
+__host__ __device__ inline int rup(int x, int m) { return (x + m - 1) / m * m; }
+
+// byte offsets of the middle-span CTA's shared memory
+struct MidSmem {
+  int fc0, fs0, Wp, S, alpha, m_run, l_run, cst, rotc, rots, dltc, dlts, ph, dJ, qn, kofs, klen, vofs, kbuf, vbuf, total;
+};
+__host__ __device__ inline MidSmem mid_smem(int J, int N, int HGp, int kvh, int pitchK, int pitchV, int qpitch) {
+  MidSmem s;
+  int o = 0;
+  auto take = [&](int bytes) {
+    int r = o;
+    o += rup(bytes, 16);
+    return r;
+  };
+  s.fc0 = take(J * (N + 1) * 4);
+  s.fs0 = take(J * (N + 1) * 4);
+  s.Wp = take(2 * N * HGp * 4);
+  s.S = take(J * HGp * 4);
+  s.alpha = take(HGp * 4);
+  s.m_run = take(HGp * 4);
+  s.l_run = take(HGp * 4);
+  s.cst = take(HGp * 4);
+  s.rotc = take(N * 4);
+  s.rots = take(N * 4);
+  s.dltc = take(N * 4);
+  s.dlts = take(N * 4);
+  s.ph = take(N * 4);
+  s.dJ = take(N * 4);
+  s.qn = take(HGp * qpitch * 4);
+  s.kofs = take((kvh + 1) * 4);
+  s.klen = take((kvh + 1) * 4);
+  s.vofs = take((kvh + 1) * 4);
+  s.kbuf = take(2 * J * pitchK * 2);
+  s.vbuf = take(2 * J * pitchV * 2);
+  s.total = o;
+  return s;
+}
+
+__host__ __device__ inline int il_smem_bytes(int TR, int F, int Hq, int Hqp, int D) {
+  return 2 * TR * (F + 8) * 2 + Hq * D * 4 + TR * Hqp * 4 + 3 * Hqp * 4;
+}
+
+// ---------------------------------------------------------------------------------------------
+// prepare: w[b,h,n] = (c2/N) sum_c C_k[b,n,c] scale_k[b,c] q[b,h,dim(c)],  cst[b,h] likewise
+// ---------------------------------------------------------------------------------------------
+constexpr int PR_ROWS = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(DEC_THREADS) decode_prepare_kernel(const __grid_constant__ DecodeParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const fa_decode_args_t& a = p.a;
+  const int b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int R = p.R, D = a.D, Mc = a.Mc_k, N = a.N, Hkv = a.Hkv;
+  float* qs = reinterpret_cast<float*>(smem_raw);                   // [R][Mc]
+  int* kch = reinterpret_cast<int*>(qs + (size_t)R * Mc);           // [Hkv+1]
+  const T* q = reinterpret_cast<const T*>(a.q) + (int64_t)b * a.q_sb;
+  for (int i = tid; i <= Hkv; i += DEC_THREADS) kch[i] = a.kc_h[i];
+  __syncthreads();
+  for (int c = tid; c < Mc; c += DEC_THREADS) {
+    int g = 0;
+    while (g + 1 < Hkv && c >= kch[g + 1]) ++g;
+    const int d = a.kc_list[c] - g * D;
+    const float sc = a.scale_k[(int64_t)b * Mc + c];
+    for (int r = 0; r < R; ++r) qs[r * Mc + c] = to_f32(q[(g * R + r) * D + d]) * sc;
+  }
+  __syncthreads();
+  const float* Ck = a.k_coef + (int64_t)b * 2 * N * Mc;
+  const float wscale = p.c2 / (float)N;
+  const int row_end = min(2 * N, (int)(blockIdx.x + 1) * PR_ROWS);
+  for (int row = blockIdx.x * PR_ROWS + warp; row < row_end; row += DEC_THREADS / 32) {
+    const float* cr = Ck + (int64_t)row * Mc;
+    for (int g = 0; g < Hkv; ++g) {
+      float acc[R_MAX];
+#pragma unroll
+      for (int r = 0; r < R_MAX; ++r) acc[r] = 0.f;
+      for (int c = kch[g] + lane; c < kch[g + 1]; c += 32) {
+        const float cv = cr[c];
+#pragma unroll
+        for (int r = 0; r < R_MAX; ++r)
+          if (r < R) acc[r] = fmaf(cv, qs[r * Mc + c], acc[r]);
+      }
+#pragma unroll
+      for (int r = 0; r < R_MAX; ++r) {
+        if (r < R) {
+          const float v = warp_sum(acc[r]);
+          if (lane == 0) p.w[((int64_t)b * a.Hq + g * R + r) * 2 * N + row] = v * wscale;
+        }
+      }
+    }
+  }
+  if (blockIdx.x == 0) {
+    for (int h = warp; h < a.Hq; h += DEC_THREADS / 32) {
+      const int g = h / R;
+      float acc = 0.f;
+      for (int c = kch[g] + lane; c < kch[g + 1]; c += 32) {
+        const int d = a.kc_list[c] - g * D;
+        const int64_t o = (int64_t)b * Mc + c;
+        acc = fmaf(to_f32(q[h * D + d]), a.avg_k_u[o] - a.avg_k_d[o] * a.scale_k[o], acc);
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) p.cst[(int64_t)b * a.Hq + h] = acc * p.c2;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// main, part 1: sinks + window rows (dense K/V rows, all heads of the rank)
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void il_issue_tile(const DecodeParams& p, int b, const void* sink, const void* win,
+                                              int row0, int row_end, T* dst, int TR, int F, int tid) {
+  const fa_decode_args_t& a = p.a;
+  const int pitch = F + 8;
+  const int cpr = F / 8;  // 16-byte chunks per row
+  const T* sb = reinterpret_cast<const T*>(sink) + (int64_t)b * a.sink_sb;
+  const T* wb = reinterpret_cast<const T*>(win) + (int64_t)b * a.win_sb;
+  for (int e = tid; e < TR * cpr; e += DEC_THREADS) {
+    const int r = e / cpr, c = e - r * cpr;
+    const int row = row0 + r;
+    T* d = dst + r * pitch + c * 8;
+    if (row < row_end) {
+      const T* src = (row < a.n_sink) ? sb + (int64_t)row * F : wb + (int64_t)(row - a.n_sink) * F;
+      cp_async16(d, src + c * 8);
+    } else {
+      *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+}
+
+template <typename T>
+__device__ void il_chunk(const DecodeParams& p, int b, int chunk, unsigned char* smem) {
+  const fa_decode_args_t& a = p.a;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int F = p.F, D = a.D, Hq = a.Hq, Hkv = a.Hkv, R = p.R, TR = p.TR, Hqp = p.Hqp;
+  const int pitch = F + 8;
+  T* ks = reinterpret_cast<T*>(smem);
+  T* vs = ks + TR * pitch;
+  float* qs = reinterpret_cast<float*>(vs + TR * pitch);  // [Hq][D], pre-scaled by c2
+  float* S = qs + Hq * D;                                   // [TR][Hqp]
+  float* m_run = S + TR * Hqp;
+  float* l_run = m_run + Hqp;
+  float* alpha = l_run + Hqp;
+
+  const int r0 = chunk * p.il_chunk_rows;
+  const int r1 = min(p.n_il, r0 + p.il_chunk_rows);
+  const int nt = (r1 - r0 + TR - 1) / TR;
+
+  il_issue_tile<T>(p, b, a.k_sink, a.k_win, r0, r1, ks, TR, F, tid);
+  cp_async_commit();
+  il_issue_tile<T>(p, b, a.v_sink, a.v_win, r0, r1, vs, TR, F, tid);
+  cp_async_commit();
+
+  const T* q = reinterpret_cast<const T*>(a.q) + (int64_t)b * a.q_sb;
+  for (int i = tid; i < Hq * D; i += DEC_THREADS) qs[i] = to_f32(q[i]) * p.c2;
+  for (int h = tid; h < Hqp; h += DEC_THREADS) {
+    m_run[h] = NEG_BIG;
+    l_run[h] = 0.f;
+    alpha[h] = 1.f;
+  }
+
+  float oacc[IT_IL][R_MAX][4];
+#pragma unroll
+  for (int i = 0; i < IT_IL; ++i)
+#pragma unroll
+    for (int r = 0; r < R_MAX; ++r)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) oacc[i][r][k] = 0.f;
+
+  for (int t = 0; t < nt; ++t) {
+    const int row0 = r0 + t * TR;
+    const int valid = min(TR, r1 - row0);
+    cp_async_wait<1>();
+    __syncthreads();
+    // ---- scores -------------------------------------------------------------------------
+    for (int it = tid; it < TR * Hkv; it += DEC_THREADS) {
+      const int row = it % TR, g = it / TR;
+      float acc[R_MAX];
+#pragma unroll
+      for (int r = 0; r < R_MAX; ++r) acc[r] = 0.f;
+      const T* kr = ks + row * pitch + g * D;
+      for (int d0 = 0; d0 < D; d0 += 8) {
+        float kf[8];
+        unpack8<T>(*reinterpret_cast<const uint4*>(kr + d0), kf);
+#pragma unroll
+        for (int r = 0; r < R_MAX; ++r) {
+          if (r < R) {
+            const float* qp = qs + (g * R + r) * D + d0;
+            const float4 q0 = *reinterpret_cast<const float4*>(qp);
+            const float4 q1 = *reinterpret_cast<const float4*>(qp + 4);
+            acc[r] += kf[0] * q0.x + kf[1] * q0.y + kf[2] * q0.z + kf[3] * q0.w + kf[4] * q1.x + kf[5] * q1.y +
+                      kf[6] * q1.z + kf[7] * q1.w;
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R_MAX; ++r)
+        if (r < R) S[row * Hqp + g * R + r] = acc[r];
+    }
+    __syncthreads();
+    if (t + 1 < nt) il_issue_tile<T>(p, b, a.k_sink, a.k_win, row0 + TR, r1, ks, TR, F, tid);
+    cp_async_commit();
+    // ---- online softmax, one warp per head ----------------------------------------------
+    for (int h = warp; h < Hq; h += DEC_THREADS / 32) {
+      float mt = NEG_BIG;
+      for (int row = lane; row < valid; row += 32) mt = fmaxf(mt, S[row * Hqp + h]);
+      mt = warp_max(mt);
+      const float m_old = m_run[h];
+      const float m_new = fmaxf(m_old, mt);
+      float lt = 0.f;
+      for (int row = lane; row < TR; row += 32) {
+        const float pv = (row < valid) ? exp2f(S[row * Hqp + h] - m_new) : 0.f;
+        S[row * Hqp + h] = pv;
+        lt += pv;
+      }
+      lt = warp_sum(lt);
+      if (lane == 0) {
+        const float al = exp2f(m_old - m_new);
+        alpha[h] = al;
+        l_run[h] = l_run[h] * al + lt;
+        m_run[h] = m_new;
+      }
+    }
+    cp_async_wait<1>();
+    __syncthreads();
+    // ---- PV -----------------------------------------------------------------------------
+#pragma unroll
+    for (int i = 0; i < IT_IL; ++i) {
+      const int f = (tid + i * DEC_THREADS) * 4;
+      if (f < F) {
+        const int g = f / D;
+#pragma unroll
+        for (int r = 0; r < R_MAX; ++r) {
+          if (r < R) {
+            const float al = alpha[g * R + r];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) oacc[i][r][k] *= al;
+          }
+        }
+        for (int row = 0; row < TR; ++row) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(vs + row * pitch + f);
+          using P2 = typename Pack2<T>::type;
+          const P2* pp = reinterpret_cast<const P2*>(&raw);
+          const float2 v01 = Pack2<T>::cvt(pp[0]), v23 = Pack2<T>::cvt(pp[1]);
+#pragma unroll
+          for (int r = 0; r < R_MAX; ++r) {
+            if (r < R) {
+              const float pv = S[row * Hqp + g * R + r];
+              oacc[i][r][0] = fmaf(pv, v01.x, oacc[i][r][0]);
+              oacc[i][r][1] = fmaf(pv, v01.y, oacc[i][r][1]);
+              oacc[i][r][2] = fmaf(pv, v23.x, oacc[i][r][2]);
+              oacc[i][r][3] = fmaf(pv, v23.y, oacc[i][r][3]);
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+    if (t + 1 < nt) il_issue_tile<T>(p, b, a.v_sink, a.v_win, row0 + TR, r1, vs, TR, F, tid);
+    cp_async_commit();
+  }
+  cp_async_wait<0>();
+
+  const int64_t slot = (int64_t)b * p.NCH + chunk;
+  for (int h = tid; h < Hq; h += DEC_THREADS) {
+    p.m_part[slot * Hq + h] = m_run[h];
+    p.l_part[slot * Hq + h] = l_run[h];
+  }
+#pragma unroll
+  for (int i = 0; i < IT_IL; ++i) {
+    const int f = (tid + i * DEC_THREADS) * 4;
+    if (f < F) {
+      const int g = f / D, d = f - g * D;
+#pragma unroll
+      for (int r = 0; r < R_MAX; ++r) {
+        if (r < R) {
+          float* o = p.o_part + (slot * Hq + g * R + r) * D + d;
+          *reinterpret_cast<float4*>(o) = make_float4(oacc[i][r][0], oacc[i][r][1], oacc[i][r][2], oacc[i][r][3]);
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// main, part 2: the middle span (verbatim dims from memory, compressed dims from w / into g)
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void mid_issue_rows(const T* base, int64_t sk, bool fast, int a0, int n8, int seg0,
+                                               int seg, int shift, int l_first, int l_end, int J, T* dst, int pitch,
+                                               int tid) {
+  if (fast) {
+    for (int e = tid; e < J * n8; e += DEC_THREADS) {
+      const int j = e / n8, c = e - j * n8;
+      const int l = l_first + j;
+      T* d = dst + j * pitch + c * 8;
+      if (l < l_end)
+        cp_async16(d, base + (int64_t)l * sk + a0 + c * 8);
+      else
+        *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  } else {
+    for (int e = tid; e < J * seg; e += DEC_THREADS) {
+      const int j = e / seg, c = e - j * seg;
+      const int l = l_first + j;
+      T v = (l < l_end) ? base[(int64_t)l * sk + seg0 + c] : T(0.f);
+      dst[j * pitch + shift + c] = v;
+    }
+  }
+}
+
+template <typename T>
+__device__ void mid_chunk(const DecodeParams& p, int b, int chunk, int group, unsigned char* smem) {
+  const fa_decode_args_t& a = p.a;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int N = a.N, D = a.D, R = p.R, J = p.J, HGp = p.HGp, Hq = a.Hq;
+  const uint32_t T_ = (uint32_t)a.T;
+  const float inv_T = 1.0f / (float)a.T;
+  const MidSmem L = mid_smem(J, N, HGp, p.kvh, p.pitchK, p.pitchV, p.qpitch);
+  float* fc0 = reinterpret_cast<float*>(smem + L.fc0);
+  float* fs0 = reinterpret_cast<float*>(smem + L.fs0);
+  float* Wp = reinterpret_cast<float*>(smem + L.Wp);
+  float* S = reinterpret_cast<float*>(smem + L.S);
+  float* alpha = reinterpret_cast<float*>(smem + L.alpha);
+  float* m_run = reinterpret_cast<float*>(smem + L.m_run);
+  float* l_run = reinterpret_cast<float*>(smem + L.l_run);
+  float* cst = reinterpret_cast<float*>(smem + L.cst);
+  float* rotc = reinterpret_cast<float*>(smem + L.rotc);
+  float* rots = reinterpret_cast<float*>(smem + L.rots);
+  float* dltc = reinterpret_cast<float*>(smem + L.dltc);
+  float* dlts = reinterpret_cast<float*>(smem + L.dlts);
+  uint32_t* ph = reinterpret_cast<uint32_t*>(smem + L.ph);
+  uint32_t* dJ = reinterpret_cast<uint32_t*>(smem + L.dJ);
+  float* qn = reinterpret_cast<float*>(smem + L.qn);
+  int* kofs = reinterpret_cast<int*>(smem + L.kofs);
+  int* klen = reinterpret_cast<int*>(smem + L.klen);
+  int* vofs = reinterpret_cast<int*>(smem + L.vofs);
+  T* kbuf = reinterpret_cast<T*>(smem + L.kbuf);
+  T* vbuf = reinterpret_cast<T*>(smem + L.vbuf);
+  const int pitchK = p.pitchK, pitchV = p.pitchV, qpitch = p.qpitch, N1 = N + 1;
+
+  // heads of this CTA
+  const int g0 = group * p.kvh;
+  const int g1 = min(a.Hkv, g0 + p.kvh);
+  const int ng = g1 - g0;
+  const int h0 = g0 * R;
+  const int nh = ng * R;
+
+  // token range
+  const int l0 = chunk * p.mid_chunk;
+  const int l1 = min(a.n_mid, l0 + p.mid_chunk);
+  const int nt = (l1 - l0 + J - 1) / J;
+
+  // verbatim column spans of this head group
+  const int seg0K = a.kn_h[g0], segK = a.kn_h[g1] - seg0K;
+  const int seg0V = a.vn_h[g0], segV = a.vn_h[g1] - seg0V;
+  const T* kbase = reinterpret_cast<const T*>(a.k_mn) + (int64_t)b * a.k_mn_sb;
+  const T* vbase = reinterpret_cast<const T*>(a.v_mn) + (int64_t)b * a.v_mn_sb;
+  const bool fastK = ((reinterpret_cast<uintptr_t>(kbase) & 15) == 0) && (a.k_mn_sk % 8 == 0);
+  const bool fastV = ((reinterpret_cast<uintptr_t>(vbase) & 15) == 0) && (a.v_mn_sk % 8 == 0);
+  const int a0K = fastK ? (seg0K & ~7) : seg0K, a0V = fastV ? (seg0V & ~7) : seg0V;
+  const int shiftK = seg0K - a0K, shiftV = seg0V - a0V;
+  const int n8K = (rup(seg0K + segK, 8) - a0K) / 8, n8V = (rup(seg0V + segV, 8) - a0V) / 8;
+
+  // first tile in flight while the tables are built
+  mid_issue_rows<T>(kbase, a.k_mn_sk, fastK, a0K, n8K, seg0K, segK, shiftK, l0, l1, J, kbuf, pitchK, tid);
+  mid_issue_rows<T>(vbase, a.v_mn_sk, fastV, a0V, n8V, seg0V, segV, shiftV, l0, l1, J, vbuf, pitchV, tid);
+  cp_async_commit();
+
+  // ---- per-CTA tables ---------------------------------------------------------------------
+  for (int e = tid; e < J * N; e += DEC_THREADS) {
+    const int j = e / N, n = e - j * N;
+    float s, c;
+    sincos_phase(phase_mod((uint64_t)j, (uint32_t)n, T_), inv_T, &s, &c);
+    fc0[j * N1 + n] = c;
+    fs0[j * N1 + n] = s;
+  }
+  for (int n = tid; n < N; n += DEC_THREADS) {
+    const uint32_t d = phase_mod((uint64_t)J, (uint32_t)n, T_);
+    dJ[n] = d;
+    float s, c;
+    sincos_phase(d, inv_T, &s, &c);
+    dltc[n] = c;
+    dlts[n] = s;
+    ph[n] = phase_mod((uint64_t)a.mid_l0 + (uint64_t)l0, (uint32_t)n, T_);
+  }
+  for (int i = tid; i <= ng; i += DEC_THREADS) {
+    kofs[i] = a.kn_h[g0 + i] - seg0K + shiftK;
+    vofs[i] = a.vn_h[g0 + i] - seg0V;  // relative to the span start (no shift)
+    if (i < ng) klen[i] = a.kn_h[g0 + i + 1] - a.kn_h[g0 + i];
+  }
+  for (int hh = tid; hh < HGp; hh += DEC_THREADS) {
+    alpha[hh] = 1.f;
+    m_run[hh] = NEG_BIG;
+    l_run[hh] = 0.f;
+    cst[hh] = (hh < nh) ? p.cst[(int64_t)b * Hq + h0 + hh] : 0.f;
+  }
+  __syncthreads();
+  {
+    // rotated weights for the first tile: W'_c = w_c cos(a) + w_s sin(a), W'_s = -w_c sin(a) + w_s cos(a)
+    const float* wb = p.w + ((int64_t)b * Hq + h0) * 2 * N;
+    for (int e = tid; e < N * HGp; e += DEC_THREADS) {
+      const int hh = e / N, n = e - hh * N;  // consecutive threads read consecutive n
+      float wc = 0.f, ws = 0.f;
+      if (hh < nh) {
+        wc = wb[(int64_t)hh * 2 * N + n];
+        ws = wb[(int64_t)hh * 2 * N + N + n];
+      }
+      float s, c;
+      sincos_phase(ph[n], inv_T, &s, &c);
+      Wp[n * HGp + hh] = wc * c + ws * s;
+      Wp[(N + n) * HGp + hh] = -wc * s + ws * c;
+    }
+    // verbatim-K query slices, pre-scaled
+    const T* q = reinterpret_cast<const T*>(a.q) + (int64_t)b * a.q_sb;
+    for (int e = tid; e < nh * qpitch; e += DEC_THREADS) {
+      const int hh = e / qpitch, i = e - hh * qpitch;
+      const int gl = hh / R;
+      float v = 0.f;
+      if (i < klen[gl]) {
+        const int d = a.kn_list[a.kn_h[g0 + gl] + i] - (g0 + gl) * D;
+        v = to_f32(q[(h0 + hh) * D + d]) * p.c2;
+      }
+      qn[hh * qpitch + i] = v;
+    }
+  }
+
+  // persistent accumulators
+  float Gc[IT_G][8], Gs[IT_G][8];
+#pragma unroll
+  for (int i = 0; i < IT_G; ++i)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) Gc[i][k] = Gs[i][k] = 0.f;
+  float ov[IT_V][R_MAX];
+  int vgl[IT_V];
+#pragma unroll
+  for (int i = 0; i < IT_V; ++i) {
+#pragma unroll
+    for (int r = 0; r < R_MAX; ++r) ov[i][r] = 0.f;
+    const int c = tid + i * DEC_THREADS;
+    int gl = 0;
+    if (c < segV)
+      while (gl + 1 < ng && c >= vofs[gl + 1]) ++gl;
+    vgl[i] = gl;
+  }
+  const int n_items_g = N * (HGp / 8);
+  __syncthreads();
+
+  for (int t = 0; t < nt; ++t) {
+    const int lt0 = l0 + t * J;
+    const int valid = min(J, l1 - lt0);
+    T* kb = kbuf + (t & 1) * J * pitchK;
+    T* vb = vbuf + (t & 1) * J * pitchV;
+    if (t + 1 < nt) {
+      T* kb2 = kbuf + ((t + 1) & 1) * J * pitchK;
+      T* vb2 = vbuf + ((t + 1) & 1) * J * pitchV;
+      mid_issue_rows<T>(kbase, a.k_mn_sk, fastK, a0K, n8K, seg0K, segK, shiftK, lt0 + J, l1, J, kb2, pitchK, tid);
+      mid_issue_rows<T>(vbase, a.v_mn_sk, fastV, a0V, n8V, seg0V, segV, shiftV, lt0 + J, l1, J, vb2, pitchV, tid);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+
+    // [A] rotation of this tile for the g update; advance the integer phases
+    for (int n = tid; n < N; n += DEC_THREADS) {
+      float s, c;
+      const uint32_t v = ph[n];
+      sincos_phase(v, inv_T, &s, &c);
+      rotc[n] = c;
+      rots[n] = s;
+      uint32_t nx = v + dJ[n];
+      if (nx >= T_) nx -= T_;
+      ph[n] = nx;
+    }
+    // [B]+[C] scores: spectral part from the base table and W', verbatim part from the K rows
+    for (int it = tid; it < J * (HGp / 4); it += DEC_THREADS) {
+      const int j = it % J, hq4 = it / J;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const float* fcr = fc0 + j * N1;
+      const float* fsr = fs0 + j * N1;
+      const float* wcol = Wp + hq4 * 4;
+#pragma unroll 4
+      for (int n = 0; n < N; ++n) {
+        const float c = fcr[n], s = fsr[n];
+        const float4 wc = *reinterpret_cast<const float4*>(wcol + n * HGp);
+        const float4 ws = *reinterpret_cast<const float4*>(wcol + (N + n) * HGp);
+        acc[0] = fmaf(c, wc.x, fmaf(s, ws.x, acc[0]));
+        acc[1] = fmaf(c, wc.y, fmaf(s, ws.y, acc[1]));
+        acc[2] = fmaf(c, wc.z, fmaf(s, ws.z, acc[2]));
+        acc[3] = fmaf(c, wc.w, fmaf(s, ws.w, acc[3]));
+      }
+      const T* krow = kb + j * pitchK;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int hh = hq4 * 4 + k;
+        float v = 0.f;
+        if (hh < nh) {
+          const int gl = hh / R;
+          const T* kr = krow + kofs[gl];
+          const float* qh = qn + hh * qpitch;
+          const int len = klen[gl];
+          float d = 0.f;
+          for (int i = 0; i < len; ++i) d = fmaf(qh[i], to_f32(kr[i]), d);
+          v = acc[k] + cst[hh] + d;
+        }
+        S[j * HGp + hh] = v;
+      }
+    }
+    __syncthreads();
+    // [D] online softmax, one warp per head
+    for (int hh = warp; hh < nh; hh += DEC_THREADS / 32) {
+      const float sv = (lane < valid) ? S[lane * HGp + hh] : NEG_BIG;
+      const float mt = warp_max(sv);
+      const float m_old = m_run[hh];
+      const float m_new = fmaxf(m_old, mt);
+      const float pv = (lane < valid) ? exp2f(sv - m_new) : 0.f;
+      if (lane < J) S[lane * HGp + hh] = pv;
+      const float lt = warp_sum(pv);
+      if (lane == 0) {
+        const float al = exp2f(m_old - m_new);
+        alpha[hh] = al;
+        l_run[hh] = l_run[hh] * al + lt;
+        m_run[hh] = m_new;
+      }
+    }
+    __syncthreads();
+    // [E] g update: tile sums against the base table, rotated into the absolute frame
+#pragma unroll
+    for (int i = 0; i < IT_G; ++i) {
+      const int item = tid + i * DEC_THREADS;
+      if (item < n_items_g) {
+        const int n = item % N, hb = item / N;
+        float tc[8], ts[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) tc[k] = ts[k] = 0.f;
+        for (int j = 0; j < J; ++j) {
+          const float c = fc0[j * N1 + n], s = fs0[j * N1 + n];
+          const float4 p0 = *reinterpret_cast<const float4*>(S + j * HGp + hb * 8);
+          const float4 p1 = *reinterpret_cast<const float4*>(S + j * HGp + hb * 8 + 4);
+          const float pa[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            tc[k] = fmaf(c, pa[k], tc[k]);
+            ts[k] = fmaf(s, pa[k], ts[k]);
+          }
+        }
+        const float rc = rotc[n], rs = rots[n];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float al = alpha[hb * 8 + k];
+          Gc[i][k] = fmaf(Gc[i][k], al, rc * tc[k] - rs * ts[k]);
+          Gs[i][k] = fmaf(Gs[i][k], al, rs * tc[k] + rc * ts[k]);
+        }
+      }
+    }
+    // [F] verbatim V numerators
+#pragma unroll
+    for (int i = 0; i < IT_V; ++i) {
+      const int c = tid + i * DEC_THREADS;
+      if (c < segV) {
+        const int gl = vgl[i];
+#pragma unroll
+        for (int r = 0; r < R_MAX; ++r)
+          if (r < R) ov[i][r] *= alpha[gl * R + r];
+        const T* vc = vb + shiftV + c;
+        for (int j = 0; j < J; ++j) {
+          const float v = to_f32(vc[j * pitchV]);
+#pragma unroll
+          for (int r = 0; r < R_MAX; ++r)
+            if (r < R) ov[i][r] = fmaf(S[j * HGp + gl * R + r], v, ov[i][r]);
+        }
+      }
+    }
+    // [G] rotate W' to the next tile
+    if (t + 1 < nt) {
+      for (int e = tid; e < N * HGp; e += DEC_THREADS) {
+        const int n = e / HGp, hh = e - n * HGp;
+        const float wc = Wp[n * HGp + hh], ws = Wp[(N + n) * HGp + hh];
+        const float dc = dltc[n], ds = dlts[n];
+        Wp[n * HGp + hh] = wc * dc + ws * ds;
+        Wp[(N + n) * HGp + hh] = ws * dc - wc * ds;
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+  // ---- chunk partials -----------------------------------------------------------------------
+  const int64_t slot = (int64_t)b * p.NCH + p.n_il_chunks + chunk;
+  for (int hh = tid; hh < nh; hh += DEC_THREADS) {
+    p.m_part[slot * Hq + h0 + hh] = m_run[hh];
+    p.l_part[slot * Hq + h0 + hh] = l_run[hh];
+  }
+  float* ob = p.o_part + (slot * Hq + h0) * D;
+  for (int e = tid; e < nh * D; e += DEC_THREADS) ob[e] = 0.f;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < IT_V; ++i) {
+    const int c = tid + i * DEC_THREADS;
+    if (c < segV) {
+      const int gl = vgl[i];
+      const int d = a.vn_list[seg0V + c] - (g0 + gl) * D;
+#pragma unroll
+      for (int r = 0; r < R_MAX; ++r)
+        if (r < R) ob[(gl * R + r) * D + d] = ov[i][r];
+    }
+  }
+  float* gb = p.g_part + (((int64_t)b * p.n_mid_chunks + chunk) * Hq + h0) * 2 * N;
+#pragma unroll
+  for (int i = 0; i < IT_G; ++i) {
+    const int item = tid + i * DEC_THREADS;
+    if (item < n_items_g) {
+      const int n = item % N, hb = item / N;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int hh = hb * 8 + k;
+        if (hh < nh) {
+          gb[(int64_t)hh * 2 * N + n] = Gc[i][k];
+          gb[(int64_t)hh * 2 * N + N + n] = Gs[i][k];
+        }
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(DEC_THREADS, 1) decode_main_kernel(const __grid_constant__ DecodeParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int b = blockIdx.y;
+  if ((int)blockIdx.x < p.n_il_chunks) {
+    il_chunk<T>(p, b, blockIdx.x, smem_raw);
+  } else {
+    const int idx = blockIdx.x - p.n_il_chunks;
+    mid_chunk<T>(p, b, idx / p.n_groups, idx % p.n_groups, smem_raw);
+  }
+}
+
+// merge weights of every chunk slot for head h:  a_i = 2^(m_i - m*)  (0 for an empty slot)
+__device__ __forceinline__ float slot_max(const DecodeParams& p, int b, int h) {
+  float ms = NEG_BIG;
+  for (int i = 0; i < p.NCH; ++i) {
+    const int64_t o = ((int64_t)b * p.NCH + i) * p.a.Hq + h;
+    if (p.l_part[o] > 0.f) ms = fmaxf(ms, p.m_part[o]);
+  }
+  return ms;
+}
+
+// ---------------------------------------------------------------------------------------------
+// contract: G*[h,n] = sum_chunks a_i g_i[h,n];  cv[rb][r][c] = sum_{n in block} G*[gR+r,n] C_v[n,c]
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(DEC_THREADS) decode_contract_kernel(const __grid_constant__ DecodeParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const fa_decode_args_t& a = p.a;
+  const int rb = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  const int N = a.N, Hq = a.Hq, R = p.R, Mc = a.Mc_v, NM = p.n_mid_chunks, rows = p.rb_rows;
+  float* am = reinterpret_cast<float*>(smem_raw);       // [NM][Hq]
+  float* Gm = am + NM * Hq;                             // [2][Hq][rows]
+  int* vch = reinterpret_cast<int*>(Gm + 2 * Hq * rows);  // [Hkv+1]
+  const int r0 = rb * rows, r1 = min(N, r0 + rows);
+  for (int i = tid; i <= a.Hkv; i += DEC_THREADS) vch[i] = a.vc_h[i];
+  for (int h = tid; h < Hq; h += DEC_THREADS) {
+    const float ms = slot_max(p, b, h);
+    for (int i = 0; i < NM; ++i) {
+      const int64_t o = ((int64_t)b * p.NCH + p.n_il_chunks + i) * Hq + h;
+      am[i * Hq + h] = (p.l_part[o] > 0.f) ? exp2f(p.m_part[o] - ms) : 0.f;
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < 2 * Hq * rows; e += DEC_THREADS) {
+    const int rr = e % rows, h = (e / rows) % Hq, half = e / (rows * Hq);
+    float acc = 0.f;
+    if (r0 + rr < r1) {
+      const int n = half * N + r0 + rr;
+      for (int i = 0; i < NM; ++i)
+        acc = fmaf(am[i * Hq + h], p.g_part[(((int64_t)b * NM + i) * Hq + h) * 2 * N + n], acc);
+    }
+    Gm[e] = acc;
+  }
+  __syncthreads();
+  const float* Cv = a.v_coef + (int64_t)b * 2 * N * Mc;
+  for (int c = tid; c < Mc; c += DEC_THREADS) {
+    int g = 0;
+    while (g + 1 < a.Hkv && c >= vch[g + 1]) ++g;
+    float acc[R_MAX];
+#pragma unroll
+    for (int r = 0; r < R_MAX; ++r) acc[r] = 0.f;
+    for (int rr = 0; rr < r1 - r0; ++rr) {
+      const float cc = Cv[(int64_t)(r0 + rr) * Mc + c];
+      const float cs = Cv[(int64_t)(N + r0 + rr) * Mc + c];
+#pragma unroll
+      for (int r = 0; r < R_MAX; ++r) {
+        if (r < R) {
+          const int h = g * R + r;
+          acc[r] = fmaf(Gm[h * rows + rr], cc, fmaf(Gm[(Hq + h) * rows + rr], cs, acc[r]));
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R_MAX; ++r)
+      if (r < R) p.cv_part[(((int64_t)b * p.n_rb + rb) * R + r) * Mc + c] = acc[r];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// output: merge numerators / denominators, add the compressed-V dims, normalise
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) decode_output_kernel(const __grid_constant__ DecodeParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const fa_decode_args_t& a = p.a;
+  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  const int D = a.D, Hq = a.Hq, R = p.R, N = a.N, Mc = a.Mc_v, NCH = p.NCH;
+  float* aw = reinterpret_cast<float*>(smem_raw);  // [NCH]
+  float* O = aw + NCH;                             // [D]
+  __shared__ float s_L, s_P, s_ms;
+  const int g = h / R, r = h - g * R;
+  if (tid < 32) {
+    // one warp computes the weights
+    float ms = NEG_BIG;
+    for (int i = tid; i < NCH; i += 32) {
+      const int64_t o = ((int64_t)b * NCH + i) * Hq + h;
+      if (p.l_part[o] > 0.f) ms = fmaxf(ms, p.m_part[o]);
+    }
+    ms = warp_max(ms);
+    float Ls = 0.f, Ps = 0.f;
+    for (int i = tid; i < NCH; i += 32) {
+      const int64_t o = ((int64_t)b * NCH + i) * Hq + h;
+      const float l = p.l_part[o];
+      const float w = (l > 0.f) ? exp2f(p.m_part[o] - ms) : 0.f;
+      aw[i] = w;
+      Ls = fmaf(w, l, Ls);
+      if (i >= p.n_il_chunks) Ps = fmaf(w, l, Ps);
+    }
+    Ls = warp_sum(Ls);
+    Ps = warp_sum(Ps);
+    if (tid == 0) {
+      s_L = Ls;
+      s_P = Ps;
+      s_ms = ms;
+    }
+  }
+  __syncthreads();
+  for (int d = tid; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int i = 0; i < NCH; ++i) acc = fmaf(aw[i], p.o_part[(((int64_t)b * NCH + i) * Hq + h) * D + d], acc);
+    O[d] = acc;
+  }
+  __syncthreads();
+  const float P = s_P, L = s_L;
+  if (a.n_mid > 0) {
+    const int c0 = a.vc_h[g], c1 = a.vc_h[g + 1];
+    for (int c = c0 + tid; c < c1; c += blockDim.x) {
+      float s = 0.f;
+      for (int rb = 0; rb < p.n_rb; ++rb) s += p.cv_part[(((int64_t)b * p.n_rb + rb) * R + r) * Mc + c];
+      const int64_t o = (int64_t)b * Mc + c;
+      const float oc = a.scale_v[o] * (s / (float)N - a.avg_v_d[o] * P) + a.avg_v_u[o] * P;
+      const int d = a.vc_list[c] - g * D;
+      O[d] += oc;  // each compressed dim belongs to exactly one column
+    }
+  }
+  __syncthreads();
+  const float inv = 1.0f / L;
+  for (int d = tid; d < D; d += blockDim.x) a.out[((int64_t)b * Hq + h) * D + d] = O[d] * inv;
+  if (tid == 0) {
+    if (a.m_out) a.m_out[(int64_t)b * Hq + h] = s_ms;
+    if (a.l_out) a.l_out[(int64_t)b * Hq + h] = L;
+  }
+}
+
+// log-sum-exp merge of normalised partial results
+__global__ void merge_kernel(const float* __restrict__ o, const float* __restrict__ m, const float* __restrict__ l,
+                             int n_parts, int rows, int D, float* __restrict__ out) {
+  const int row = blockIdx.x;
+  float ms = NEG_BIG;
+  for (int i = 0; i < n_parts; ++i)
+    if (l[(int64_t)i * rows + row] > 0.f) ms = fmaxf(ms, m[(int64_t)i * rows + row]);
+  float den = 0.f;
+  for (int i = 0; i < n_parts; ++i) {
+    const float li = l[(int64_t)i * rows + row];
+    if (li > 0.f) den += li * exp2f(m[(int64_t)i * rows + row] - ms);
+  }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int i = 0; i < n_parts; ++i) {
+      const float li = l[(int64_t)i * rows + row];
+      if (li > 0.f) acc = fmaf(li * exp2f(m[(int64_t)i * rows + row] - ms), o[((int64_t)i * rows + row) * D + d], acc);
+    }
+    out[(int64_t)row * D + d] = acc / den;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side: plan, validation, launches
+// ---------------------------------------------------------------------------------------------
+constexpr int SMEM_LIMIT = 200 * 1024;
+
+static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
+  FA_REQUIRE(a.B > 0 && a.Hq > 0 && a.Hkv > 0 && a.D > 0, FA_ERR_SHAPE, "fa_decode_attn: B, Hq, Hkv, D must be positive");
+  FA_REQUIRE(a.Hq % a.Hkv == 0, FA_ERR_SHAPE, "fa_decode_attn: Hq (%d) must be a multiple of Hkv (%d)", a.Hq, a.Hkv);
+  FA_REQUIRE(a.dtype == FA_DTYPE_F16 || a.dtype == FA_DTYPE_BF16, FA_ERR_DTYPE, "fa_decode_attn: bad dtype %d", a.dtype);
+  FA_REQUIRE(a.n_sink >= 0 && a.n_win >= 0 && a.n_mid >= 0 && a.n_sink + a.n_win + a.n_mid > 0, FA_ERR_SHAPE,
+             "fa_decode_attn: no keys to attend");
+  FA_REQUIRE(a.D % 8 == 0, FA_ERR_ALIGN, "fa_decode_attn: head_dim (%d) must be a multiple of 8", a.D);
+  p.a = a;
+  p.R = a.Hq / a.Hkv;
+  FA_REQUIRE(p.R <= R_MAX, FA_ERR_CAPACITY, "fa_decode_attn: at most %d query heads per KV head (got %d)", R_MAX, p.R);
+  p.F = a.Hkv * a.D;
+  FA_REQUIRE(p.F <= 2048, FA_ERR_CAPACITY, "fa_decode_attn: Hkv*D (%d) exceeds 2048", p.F);
+  p.n_il = a.n_sink + a.n_win;
+  const float sc = (a.sm_scale > 0.f) ? a.sm_scale : 1.0f / sqrtf((float)a.D);
+  p.c2 = sc * 1.4426950408889634f;
+  p.Hqp = rup(a.Hq, 4);
+  // sinks + window tiles
+  int TR = 128;
+  while (TR > 8 && TR * p.F > 32768) TR >>= 1;
+  p.TR = TR;
+  const int il_smem = il_smem_bytes(TR, p.F, a.Hq, p.Hqp, a.D);
+  p.n_il_chunks = p.n_il > 0 ? ceil_div(p.n_il, 256) : 0;
+  p.il_chunk_rows = p.n_il > 0 ? rup(ceil_div(p.n_il, p.n_il_chunks), TR) : TR;
+  p.n_il_chunks = p.n_il > 0 ? ceil_div(p.n_il, p.il_chunk_rows) : 0;
+
+  int mid_smem_bytes = 0;
+  p.J = 8; p.kvh = 1; p.HG = p.R; p.HGp = 8; p.n_groups = 1; p.pitchK = p.pitchV = 16; p.qpitch = 4;
+  p.n_mid_chunks = 0; p.mid_chunk = 8; p.n_rb = 0; p.rb_rows = 1;
+  if (a.n_mid > 0) {
+    FA_REQUIRE(a.N > 0 && a.T > 0, FA_ERR_SHAPE, "fa_decode_attn: N and T must be positive");
+    FA_REQUIRE(a.N <= 1024, FA_ERR_CAPACITY, "fa_decode_attn: N (%d) exceeds 1024", a.N);
+    FA_REQUIRE(a.Mc_k >= 0 && a.Mn_k >= 0 && a.Mc_k + a.Mn_k == p.F && a.Mc_v >= 0 && a.Mn_v >= 0 &&
+                   a.Mc_v + a.Mn_v == p.F, FA_ERR_SHAPE,
+               "fa_decode_attn: compressed + verbatim dims must add up to Hkv*D for K and for V");
+    FA_REQUIRE(a.k_mn_sk >= a.Mn_k && a.v_mn_sk >= a.Mn_v, FA_ERR_SHAPE, "fa_decode_attn: verbatim row stride too small");
+    int J = 32;
+    while (J > 8 && J * a.N > 8192) J >>= 1;
+    p.J = J;
+    bool ok = false;
+    for (int kvh = a.Hkv; kvh >= 1; --kvh) {
+      const int HG = kvh * p.R, HGp = rup(HG, 8);
+      if ((int64_t)HGp * 2 * a.N > 16384) continue;           // W' and the g accumulators
+      if ((int64_t)a.N * (HGp / 8) > IT_G * DEC_THREADS) continue;
+      const int boundK = a.Mn_k < kvh * a.D ? a.Mn_k : kvh * a.D;
+      const int boundV = a.Mn_v < kvh * a.D ? a.Mn_v : kvh * a.D;
+      if (boundV > IT_V * DEC_THREADS) continue;
+      const int pitchK = rup(boundK, 8) + 16, pitchV = rup(boundV, 8) + 16;
+      const int qpitch = rup((a.Mn_k < a.D ? a.Mn_k : a.D) + 1, 4);
+      const MidSmem L = mid_smem(J, a.N, HGp, kvh, pitchK, pitchV, qpitch);
+      if (L.total > SMEM_LIMIT) continue;
+      p.kvh = kvh; p.HG = HG; p.HGp = HGp; p.pitchK = pitchK; p.pitchV = pitchV; p.qpitch = qpitch;
+      p.n_groups = ceil_div(a.Hkv, kvh);
+      mid_smem_bytes = L.total;
+      ok = true;
+      break;
+    }
+    FA_REQUIRE(ok, FA_ERR_UNSUPPORTED, "fa_decode_attn: no head grouping fits shared memory (N=%d, R=%d, D=%d)", a.N,
+               p.R, a.D);
+    const int sms = sm_count();
+    int target = (3 * sms) / (a.B * p.n_groups) - p.n_il_chunks;
+    const int max_chunks = ceil_div(a.n_mid, J);
+    if (target < 1) target = 1;
+    if (target > max_chunks) target = max_chunks;
+    p.mid_chunk = rup(ceil_div(a.n_mid, target), J);
+    p.n_mid_chunks = ceil_div(a.n_mid, p.mid_chunk);
+    int nrb = ceil_div(2 * sms, a.B);
+    if (nrb > a.N) nrb = a.N;
+    if (nrb < 1) nrb = 1;
+    p.rb_rows = ceil_div(a.N, nrb);
+    p.n_rb = ceil_div(a.N, p.rb_rows);
+  }
+  p.NCH = p.n_il_chunks + p.n_mid_chunks;
+  p.smem_main = il_smem > mid_smem_bytes ? il_smem : mid_smem_bytes;
+  if (p.n_il == 0) p.smem_main = mid_smem_bytes;
+  FA_REQUIRE(p.smem_main <= 227 * 1024, FA_ERR_CAPACITY, "fa_decode_attn: shared memory need %d exceeds 227 KB", p.smem_main);
+  p.smem_prepare = (p.R * a.Mc_k) * 4 + (a.Hkv + 1) * 4;
+  p.smem_contract = (p.n_mid_chunks * a.Hq + 2 * a.Hq * p.rb_rows) * 4 + (a.Hkv + 1) * 4;
+  FA_REQUIRE(p.smem_prepare <= SMEM_LIMIT && p.smem_contract <= SMEM_LIMIT, FA_ERR_CAPACITY,
+             "fa_decode_attn: helper kernels exceed shared memory");
+  // scratch layout (floats, each block 16-byte aligned)
+  int64_t o = 0;
+  auto take = [&](int64_t n) {
+    int64_t r = o;
+    o += (n + 3) / 4 * 4;
+    return r;
+  };
+  const int64_t B = a.B, Hq = a.Hq;
+  const int64_t ow = take(B * Hq * 2 * a.N), oc = take(B * Hq), om = take(B * p.NCH * Hq), ol = take(B * p.NCH * Hq);
+  const int64_t oo = take(B * p.NCH * Hq * a.D), og = take(B * p.n_mid_chunks * Hq * 2 * a.N);
+  const int64_t ov = take(B * p.n_rb * p.R * a.Mc_v);
+  p.scratch_floats = o;
+  float* s = reinterpret_cast<float*>(a.scratch);
+  p.w = s + ow; p.cst = s + oc; p.m_part = s + om; p.l_part = s + ol; p.o_part = s + oo; p.g_part = s + og;
+  p.cv_part = s + ov;
+  return FA_OK;
+}
+
+template <typename K>
+static int set_smem(K kernel, int bytes) {
+  if (bytes > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
+  }
+  return FA_OK;
+}
+
+template <typename T>
+static int launch_decode(const DecodeParams& p, cudaStream_t st) {
+  const fa_decode_args_t& a = p.a;
+  int rc;
+  auto mark = [&](int i) {
+    if (a.phase_events_host) cudaEventRecord((cudaEvent_t)a.phase_events_host[i], st);
+  };
+  mark(0);
+  if (a.n_mid > 0) {
+    if ((rc = set_smem(decode_prepare_kernel<T>, p.smem_prepare)) != FA_OK) return rc;
+    dim3 g1(ceil_div(2 * a.N, PR_ROWS), a.B);
+    decode_prepare_kernel<T><<<g1, DEC_THREADS, p.smem_prepare, st>>>(p);
+    FA_CHECK_LAUNCH("fa_decode_attn(prepare)");
+  }
+  mark(1);
+  if ((rc = set_smem(decode_main_kernel<T>, p.smem_main)) != FA_OK) return rc;
+  dim3 g2(p.n_il_chunks + p.n_mid_chunks * p.n_groups, a.B);
+  decode_main_kernel<T><<<g2, DEC_THREADS, p.smem_main, st>>>(p);
+  FA_CHECK_LAUNCH("fa_decode_attn(main)");
+  mark(2);
+  if (a.n_mid > 0) {
+    if ((rc = set_smem(decode_contract_kernel, p.smem_contract)) != FA_OK) return rc;
+    dim3 g3(p.n_rb, a.B);
+    decode_contract_kernel<<<g3, DEC_THREADS, p.smem_contract, st>>>(p);
+    FA_CHECK_LAUNCH("fa_decode_attn(contract)");
+  }
+  mark(3);
+  dim3 g4(a.Hq, a.B);
+  const int smem_out = (p.NCH + a.D) * 4;
+  decode_output_kernel<<<g4, 128, smem_out, st>>>(p);
+  FA_CHECK_LAUNCH("fa_decode_attn(output)");
+  mark(4);
+  return FA_OK;
+}
+
+}  // namespace fa
+
+using namespace fa;
+
+extern "C" size_t fa_decode_scratch_bytes(const fa_decode_args_t* args) {
+  if (!args) return 0;
+  DecodeParams p;
+  fa_decode_args_t a = *args;
+  a.scratch = nullptr;
+  if (make_plan(a, p) != FA_OK) return 0;
+  return (size_t)p.scratch_floats * sizeof(float);
+}
+
+extern "C" int fa_decode_attn(const fa_decode_args_t* args, fa_stream_t stream) {
+  FA_REQUIRE(args, FA_ERR_NULL, "fa_decode_attn: null argument block");
+  const fa_decode_args_t& a = *args;
+  DecodeParams p;
+  int rc = make_plan(a, p);
+  if (rc != FA_OK) return rc;
+  FA_REQUIRE(a.q && a.out, FA_ERR_NULL, "fa_decode_attn: q / out is null");
+  FA_REQUIRE(a.n_sink == 0 || (a.k_sink && a.v_sink), FA_ERR_NULL, "fa_decode_attn: sink rows are null");
+  FA_REQUIRE(a.n_win == 0 || (a.k_win && a.v_win), FA_ERR_NULL, "fa_decode_attn: window rows are null");
+  if (a.n_mid > 0) {
+    FA_REQUIRE(a.k_coef && a.v_coef && a.avg_k_u && a.avg_k_d && a.scale_k && a.avg_v_u && a.avg_v_d && a.scale_v,
+               FA_ERR_NULL, "fa_decode_attn: coefficient or statistics pointer is null");
+    FA_REQUIRE((a.Mn_k == 0 || a.k_mn) && (a.Mn_v == 0 || a.v_mn), FA_ERR_NULL, "fa_decode_attn: verbatim store is null");
+    FA_REQUIRE(a.kc_h && a.kn_h && a.vc_h && a.vn_h && (a.Mc_k == 0 || a.kc_list) && (a.Mc_v == 0 || a.vc_list) &&
+                   (a.Mn_k == 0 || a.kn_list) && (a.Mn_v == 0 || a.vn_list), FA_ERR_NULL,
+               "fa_decode_attn: index table is null");
+    FA_REQUIRE(a.mid_l0 >= 0, FA_ERR_SHAPE, "fa_decode_attn: mid_l0 must be non-negative");
+  }
+  FA_REQUIRE(a.scratch && a.scratch_bytes >= (size_t)p.scratch_floats * sizeof(float), FA_ERR_CAPACITY,
+             "fa_decode_attn: scratch too small (%zu < %zu bytes)", a.scratch_bytes,
+             (size_t)p.scratch_floats * sizeof(float));
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  FA_REQUIRE(al16(a.scratch) && al16(a.q), FA_ERR_ALIGN, "fa_decode_attn: q and scratch must be 16-byte aligned");
+  if (a.n_sink > 0)
+    FA_REQUIRE(al16(a.k_sink) && al16(a.v_sink) && a.sink_sb % 8 == 0, FA_ERR_ALIGN,
+               "fa_decode_attn: sink rows must be 16-byte aligned");
+  if (a.n_win > 0)
+    FA_REQUIRE(al16(a.k_win) && al16(a.v_win) && a.win_sb % 8 == 0, FA_ERR_ALIGN,
+               "fa_decode_attn: window rows must be 16-byte aligned");
+  FA_REQUIRE(a.q_sb % 8 == 0 || a.B == 1, FA_ERR_ALIGN, "fa_decode_attn: q batch stride must be a multiple of 8");
+  cudaStream_t st = (cudaStream_t)stream;
+  return a.dtype == FA_DTYPE_F16 ? launch_decode<__half>(p, st) : launch_decode<__nv_bfloat16>(p, st);
+}
+
+extern "C" int fa_merge(const float* o, const float* m, const float* l, int n_parts, int rows, int D, float* out,
+                        fa_stream_t stream) {
+  FA_REQUIRE(n_parts > 0 && rows > 0 && D > 0, FA_ERR_SHAPE, "fa_merge: sizes must be positive");
+  FA_REQUIRE(o && m && l && out, FA_ERR_NULL, "fa_merge: null pointer");
+  merge_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(o, m, l, n_parts, rows, D, out);
+  FA_CHECK_LAUNCH("fa_merge");
+  return FA_OK;
+}

@@ -1,0 +1,177 @@
+/*
+ * fourier_b200.h -- C ABI of the sm_100a kernels behind the Fourier-compressed KV cache.
+ *
+ * The reference (FourierAttention, fourier_attn_triton/) has no native interface: its device
+ * code is Triton launched from Python.  Each entry point below therefore names the reference
+ * Python function whose device work it replaces; "KM" is
+ * fourier_attn_triton/fourier_triton_valid4_v2.py, "CU" is
+ * fourier_attn_triton/cache_utils_fourier.py, "ML" is
+ * fourier_attn_triton/modeling_llama_fourier.py.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its name ends in _host;
+ *   - element strides are in ELEMENTS, not bytes;
+ *   - "model dtype" tensors are fp16 or bf16 (fa_dtype_t); coefficients and statistics are fp32;
+ *   - index tables are int32;
+ *   - every call is asynchronous on `stream`, allocates nothing, never synchronises, and returns
+ *     FA_OK or a negative fa_status_t; fa_last_error_string() describes the last failure of the
+ *     calling thread;
+ *   - coefficient layout (KM:68-78, KM:865): (B, 2N, Mc) fp32, rows 0..N-1 cosine sums, rows
+ *     N..2N-1 sine sums.
+ */
+#ifndef FOURIER_B200_H
+#define FOURIER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum { FA_DTYPE_F16 = 0, FA_DTYPE_BF16 = 1 } fa_dtype_t;
+
+typedef enum {
+  FA_OK = 0,
+  FA_ERR_NULL = -1,        /* a required pointer is null                       */
+  FA_ERR_SHAPE = -2,       /* a size is non-positive or inconsistent            */
+  FA_ERR_DTYPE = -3,       /* unknown fa_dtype_t                                */
+  FA_ERR_ALIGN = -4,       /* a pointer or stride breaks a stated alignment     */
+  FA_ERR_CAPACITY = -5,    /* the problem exceeds a stated maximum              */
+  FA_ERR_CUDA = -6,        /* a CUDA runtime call failed                        */
+  FA_ERR_UNSUPPORTED = -7  /* valid but not implemented for this configuration  */
+} fa_status_t;
+
+/* How the decode-time projection forms its angle.
+ * FA_ANGLE_EXACT: 2*pi*((pos*n) mod T)/T with the phase reduced in integers.
+ * FA_ANGLE_KM57 : fl32(fl32(fl32(c*pos)*n)/T), c = fl32(2*3.14159265359) -- the float32 roundings
+ *                 of the reference projection kernel (KM:57), for parity of the rank-1 updates. */
+typedef enum { FA_ANGLE_EXACT = 0, FA_ANGLE_KM57 = 1 } fa_angle_t;
+
+typedef void* fa_stream_t; /* a cudaStream_t */
+
+int fa_version(void);
+const char* fa_last_error_string(void);
+
+/* out[b,k,i] = x[b,k,idx[i]], i < n_idx, k < K.
+ * Replaces the advanced-index gathers `k_mid[:, :, list]` of CU:560-561 / CU:578-579 and the
+ * per-step `k_local[:, 0:1, list]` of CU:735 / CU:741. */
+int fa_gather_cols(const void* x, int dtype, int B, int K, int64_t x_sb, int64_t x_sk,
+                   const int32_t* idx, int n_idx, void* out, int64_t o_sb, int64_t o_sk,
+                   fa_stream_t stream);
+
+/* Column mean and one-sided maximum deviation over k < K of x[b,k,idx[m]] (idx may be null:
+ * identity).  avg/dev: (B, Mc) fp32; the caller casts to the model dtype as KM:461 does.
+ * Replaces mat_avg_std_triton (KM:433-461, kernel KM:332-430). */
+int fa_colstats(const void* x, int dtype, int B, int K, int64_t x_sb, int64_t x_sk,
+                const int32_t* idx, int Mc, float* avg, float* dev, fa_stream_t stream);
+
+/* Forward projection of K rows onto N cosines + N sines of period T_c with phase offset k_start:
+ *   coef[b,n,m]   (+)= sum_k x[b,k,idx[m]] cos(2 pi (k+k_start) n / T_c)
+ *   coef[b,N+n,m] (+)= sum_k x[b,k,idx[m]] sin(2 pi (k+k_start) n / T_c)
+ * idx may be null (identity, then x has Mc columns).  accumulate != 0 adds to coef.
+ * scratch: fp32 device buffer of at least fa_compress_scratch_bytes(...) bytes (split-K partials,
+ * reduced in a fixed order).
+ * Replaces the prefill FFT of MultiDimHiPPO2.forward (KM:857-865) and the general-K
+ * mat_fourier_triton (KM:81-102, kernel KM:21-78). */
+size_t fa_compress_scratch_bytes(int B, int K, int N, int Mc);
+int fa_compress(const void* x, int dtype, int B, int K, int64_t x_sb, int64_t x_sk,
+                const int32_t* idx, int Mc, int N, int T_c, int64_t k_start, float* coef,
+                int accumulate, void* scratch, size_t scratch_bytes, fa_stream_t stream);
+
+/* Decode-time rank-1 update for K and V in one launch (either side may be skipped with a null
+ * coefficient pointer):  coef[b,n,m] += cos(angle(phase,n)) * row[b, idx[m]], sine rows likewise.
+ * Replaces `base_input + mat_fourier_triton(slice_input, N, T_c, K_start=phase)` with K = 1
+ * (KM:855-856; call sites CU:733, CU:739). */
+int fa_evict_update(float* k_coef, const void* k_row, int64_t k_row_sb, const int32_t* k_idx, int Mc_k,
+                    float* v_coef, const void* v_row, int64_t v_row_sb, const int32_t* v_idx, int Mc_v,
+                    int dtype, int B, int N, int64_t phase, int T_c, int angle_mode,
+                    fa_stream_t stream);
+
+/* Statistics of the reconstructed span: x^[k,m] = (1/N) sum_n [coef[n,m] cos(2 pi k n/T) +
+ * coef[N+n,m] sin(2 pi k n/T)], k < K;  avg = mean_k, dev = max(max_k - avg, avg - min_k).
+ * Outputs (B, Mc) fp32; the caller casts to fp16 as KM:326 does.
+ * scratch: at least fa_recon_stats_scratch_bytes(...) bytes.
+ * Replaces mat_fourier_avg_std_triton (KM:285-326, kernel KM:189-282). */
+size_t fa_recon_stats_scratch_bytes(int B, int K, int Mc);
+int fa_recon_stats(const float* coef, int B, int N, int Mc, int K, int T, float* avg, float* dev,
+                   void* scratch, size_t scratch_bytes, fa_stream_t stream);
+
+/* Stand-alone inverse: out[m,k] = (1/N) sum_n [c[m,n] cos(2 pi k n/T) + c[m,N+n] sin(2 pi k n/T)].
+ * c: (M, 2N) fp32 row-major, out: (M, K) fp32.  Replaces mat_fourier_inv_triton (KM:170-183). */
+int fa_fourier_inverse(const float* c, int M, int N, int K, int T, float* out, fa_stream_t stream);
+
+/* One steady-state cache step for K and V (CU:735-737, CU:741-743): the verbatim dims of the
+ * evicted window row are appended to the uncompressed store and the new token row is written
+ * behind the window.
+ *   *_evict : (B, F) evicted row,   stride *_evict_sb
+ *   *_unc   : (B, 1, Mn) destination row (already offset to the append position), stride *_unc_sb
+ *   *_new   : new token, element (b, h, d) at b*new_sb + h*new_sh + d
+ *   *_dst   : (B, F) destination row in the window buffer, stride *_dst_sb */
+int fa_cache_step(const void* k_evict, const void* v_evict, int64_t evict_sb,
+                  const int32_t* kn_idx, int Mn_k, const int32_t* vn_idx, int Mn_v,
+                  void* k_unc, int64_t k_unc_sb, void* v_unc, int64_t v_unc_sb,
+                  const void* k_new, const void* v_new, int64_t new_sb, int64_t new_sh,
+                  void* k_dst, void* v_dst, int64_t dst_sb,
+                  int dtype, int B, int Hkv, int D, fa_stream_t stream);
+
+/* ---- fused decode attention over the compressed cache --------------------------------------
+ * Replaces triton_fourier_attn (KM:684-779: kernel KM:470-681 plus the PyTorch split-KV merge
+ * KM:756-776) and, in semantics, torch_fourier_attn (KM:794-837).  One query token per sequence.
+ */
+typedef struct {
+  /* geometry */
+  int32_t B, Hq, Hkv, D;
+  int32_t n_sink, n_win; /* rows of the two verbatim segments ("k_init", "k_local")          */
+  int32_t n_mid;         /* rows of the middle span held here (k_uncompressed.size(1))       */
+  int32_t mid_l0;        /* span position of row 0 of k_mn/v_mn (0 unless the span is split
+                            by sequence across devices)                                     */
+  int32_t N;             /* cosine count; coefficients have 2N rows                          */
+  int32_t T;             /* reconstruction period (ML:660)                                   */
+  int32_t Mc_k, Mn_k, Mc_v, Mn_v;
+  int32_t dtype;         /* fa_dtype_t of q, sinks, window and verbatim stores               */
+  float sm_scale;        /* softmax scale; <= 0 selects 1/sqrt(D) (KM:696)                   */
+  /* tensors */
+  const void* q;         /* (B, Hq*D), stride q_sb                                           */
+  int64_t q_sb;
+  const void *k_sink, *v_sink; /* (B, n_sink, F) strides sink_sb, F                          */
+  int64_t sink_sb;
+  const void *k_win, *v_win;   /* (B, n_win, F) strides win_sb, F                            */
+  int64_t win_sb;
+  const void *k_mn, *v_mn;     /* (B, n_mid, Mn_*) batch strides *_mn_sb, row strides *_mn_sk  */
+  int64_t k_mn_sb, v_mn_sb;
+  int64_t k_mn_sk, v_mn_sk;    /* >= Mn_*; rows whose start is 16-byte aligned stream fastest   */
+  const float *k_coef, *v_coef; /* (B, 2N, Mc_*) contiguous                                  */
+  const float *avg_k_u, *avg_k_d, *scale_k; /* (B, Mc_k) contiguous fp32                     */
+  const float *avg_v_u, *avg_v_d, *scale_v; /* (B, Mc_v) contiguous fp32                     */
+  /* index tables (CU:444-452): flat dims and cumulative per-head offsets with leading 0      */
+  const int32_t *kc_list, *kc_h, *kn_list, *kn_h, *vc_list, *vc_h, *vn_list, *vn_h;
+  /* output */
+  float* out;            /* (B, Hq, D) fp32 contiguous                                        */
+  /* optional softmax statistics for a cross-device merge (fa_merge): per (b, h) the maximum
+   * score in the log2 domain and the denominator relative to it                               */
+  float* m_out;          /* (B, Hq) or null                                                   */
+  float* l_out;          /* (B, Hq) or null                                                   */
+  /* scratch */
+  void* scratch;
+  size_t scratch_bytes;
+  /* optional profiling aid: a HOST array of five cudaEvent_t recorded on `stream` before the first
+   * launch and after each of the four launches (prepare, main, contract, output); null = off   */
+  void* const* phase_events_host;
+} fa_decode_args_t;
+
+/* Bytes of scratch fa_decode_attn needs for this geometry (only the size fields are read). */
+size_t fa_decode_scratch_bytes(const fa_decode_args_t* args_host);
+int fa_decode_attn(const fa_decode_args_t* args_host, fa_stream_t stream);
+
+/* Log-sum-exp merge of n_parts partial results (KM:756-776), e.g. one per device of a
+ * sequence split:  out = sum_i o_i l_i 2^(m_i - m*) / sum_i l_i 2^(m_i - m*),
+ * with o_i the NORMALISED partial outputs (rows, D), m_i/l_i (rows).  parts are stacked:
+ * o: (n_parts, rows, D), m, l: (n_parts, rows). */
+int fa_merge(const float* o, const float* m, const float* l, int n_parts, int rows, int D,
+             float* out, fa_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FOURIER_B200_H */

@@ -1,0 +1,232 @@
+"""Kernel-level GPU parity through the C ABI wrappers: every kernel against the CPU oracle on seeded
+inputs, including ragged index sets, odd sizes, both periods and the sharded forms."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import fourier_oracle as fo
+from tests.gpu_util import TDT, decode_inputs_from_oracle, dev, host, oracle_cache
+from tests.helpers import attn_err_excess, case_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def _geom(**kw):
+    g = dict(B=1, Hq=4, Hkv=2, D=16, S=2, W=7, M=8, P=64, steps=2, mpe=1 << 20, dtype="fp16", ncomp=12,
+             ragged=False, seed=100)
+    g.update(kw)
+    return g
+
+
+DECODE_CASES = {
+    "tiny": _geom(),
+    "ragged_heads": _geom(B=2, Hq=8, Hkv=4, D=32, W=9, M=16, P=150, ragged=True, seed=101),
+    "gqa3_bf16": _geom(B=2, Hq=6, Hkv=2, D=64, W=17, M=32, P=333, dtype="bf16", ncomp=40, seed=102),
+    "mha": _geom(B=1, Hq=4, Hkv=4, D=8, S=0, W=4, M=8, P=50, ncomp=5, seed=103),
+    "one_kv_head": _geom(B=3, Hq=4, Hkv=1, D=128, S=4, W=33, M=64, P=700, ncomp=96, seed=104),
+    "wide": _geom(B=2, Hq=32, Hkv=8, D=128, S=4, W=64, M=128, P=1200, ncomp=96, seed=105),
+    "many_states": _geom(B=1, Hq=8, Hkv=2, D=64, S=4, W=40, M=1024, P=2400, ncomp=48, seed=106),
+    "max_states": _geom(B=1, Hq=8, Hkv=2, D=32, S=1, W=8, M=2048, P=2200, ncomp=24, seed=107),
+    "llama3b_shape": _geom(B=2, Hq=24, Hkv=8, D=128, S=4, W=48, M=256, P=900, dtype="bf16", ncomp=80, seed=108),
+    "nothing_verbatim": _geom(B=1, Hq=4, Hkv=2, D=16, W=6, M=8, P=70, ncomp=16, seed=109),
+    "nothing_compressed": _geom(B=1, Hq=4, Hkv=2, D=16, W=6, M=8, P=70, ncomp=0, seed=110),
+}
+
+
+def _state(g):
+    tables, k, v, qs = case_inputs(g)
+    oc = oracle_cache(g, tables)
+    P = g["P"]
+    oc.update(k[:, :, :P], v[:, :, :P], 0)
+    oc.update(k[:, :, P:P + 1], v[:, :, P:P + 1], 0)
+    return oc, qs[0]
+
+
+@pytest.mark.parametrize("name", list(DECODE_CASES))
+@pytest.mark.parametrize("pad_rows", [True, False])
+def test_decode_attn_matches_oracle(name, pad_rows):
+    import fourierattention_b200.ops as ops
+    g = DECODE_CASES[name]
+    oc, q = _state(g)
+    inp = decode_inputs_from_oracle(oc, g["dtype"], pad_rows=pad_rows)
+    out = ops.decode_attn(dev(q, g["dtype"]), num_head_q=g["Hq"], num_head_kv=g["Hkv"], T=oc.T, **inp)
+    ideal = oc.attend(q, 0, g["Hq"], g["Hkv"], faithful=False)[:, :, 0]
+    err = np.abs(host(out) - ideal).max()
+    assert err <= 3e-5 * max(1.0, np.abs(ideal).max()), err
+    ref = oc.attend(q, 0, g["Hq"], g["Hkv"], faithful=True)[:, :, 0]
+    assert attn_err_excess(host(out), ref, g["dtype"]) <= 0
+
+
+def test_decode_attn_reference_entry_point():
+    """triton_fourier_attn with the reference's argument list (concatenated sinks+window, int64 lists)."""
+    from fourierattention_b200.fourier_triton_valid4_v2 import torch_fourier_attn, triton_fourier_attn
+    g = DECODE_CASES["ragged_heads"]
+    oc, q = _state(g)
+    kc, vc, tb, dt = oc.key_cache[0], oc.value_cache[0], oc.tables[0], g["dtype"]
+    i64 = lambda a: torch.as_tensor(np.asarray(a), dtype=torch.int64, device="cuda")
+    args = dict(
+        q=dev(q, dt).view(g["B"], 1, -1),
+        k_il=dev(np.concatenate([kc["k_init"], kc["k_local"]], 1), dt),
+        v_il=dev(np.concatenate([vc["v_init"], vc["v_local"]], 1), dt),
+        k_mc=dev(kc["k_compressed"]), v_mc=dev(vc["v_compressed"]),
+        k_mn=dev(kc["k_uncompressed"], dt), v_mn=dev(vc["v_uncompressed"], dt),
+        avg_k_u=dev(oc.k_layer_average[0], dt), avg_k_d=dev(oc.kd_layer_average[0], "fp16"),
+        scale_k=dev(oc.k_scale[0], "fp16"), avg_v_u=dev(oc.v_layer_average[0], dt),
+        avg_v_d=dev(oc.vd_layer_average[0], "fp16"), scale_v=dev(oc.v_scale[0], "fp16"),
+        kc_list=i64(tb.kc), kc_h_list=i64(tb.kc_h), kn_list=i64(tb.kn), kn_h_list=i64(tb.kn_h),
+        vc_list=i64(tb.vc), vc_h_list=i64(tb.vc_h), vn_list=i64(tb.vn), vn_h_list=i64(tb.vn_h),
+        num_head_q=g["Hq"], num_head_kv=g["Hkv"], seq_len_m=kc["k_uncompressed"].shape[1], T=oc.T)
+    o = triton_fourier_attn(**args)
+    assert tuple(o.shape) == (g["B"], g["Hq"], 1, g["D"]) and o.dtype == torch.float32
+    ideal = oc.attend(q, 0, g["Hq"], g["Hkv"], faithful=False)
+    assert np.abs(host(o) - ideal).max() <= 3e-5
+    o16 = torch_fourier_attn(**args)
+    assert o16.dtype == torch.float16
+    with pytest.raises(AssertionError):
+        args["q"] = args["q"].expand(g["B"], 2, -1)
+        triton_fourier_attn(**args)
+
+
+def test_head_shards_equal_full():
+    """Each KV-head shard attends on its own; concatenating the shard outputs gives the full result."""
+    import fourierattention_b200.ops as ops
+    g = DECODE_CASES["ragged_heads"]
+    oc, q = _state(g)
+    dt, D, R = g["dtype"], g["D"], g["Hq"] // g["Hkv"]
+    full = host(ops.decode_attn(dev(q, dt), num_head_q=g["Hq"], num_head_kv=g["Hkv"], T=oc.T,
+                                **decode_inputs_from_oracle(oc, dt)))
+    kc, vc, tb = oc.key_cache[0], oc.value_cache[0], oc.tables[0]
+    for h0, h1 in ((0, 1), (1, 3), (3, 4)):
+        sl = slice(h0 * D, h1 * D)
+        sub = lambda lst, cum: (np.asarray(lst[cum[h0]:cum[h1]]) - h0 * D, np.asarray(cum[h0:h1 + 1]) - cum[h0])
+        kcl, kch = sub(tb.kc, tb.kc_h); knl, knh = sub(tb.kn, tb.kn_h)
+        vcl, vch = sub(tb.vc, tb.vc_h); vnl, vnh = sub(tb.vn, tb.vn_h)
+        f32 = lambda a: dev(np.ascontiguousarray(np.asarray(a, np.float32)))
+        tabs = ops.DecodeTables(kcl, kch, knl, knh, vcl, vch, vnl, vnh, device="cuda")
+        ck, cv = slice(tb.kc_h[h0], tb.kc_h[h1]), slice(tb.vc_h[h0], tb.vc_h[h1])
+        nk, nv = slice(tb.kn_h[h0], tb.kn_h[h1]), slice(tb.vn_h[h0], tb.vn_h[h1])
+        qs = q.reshape(g["B"], g["Hq"], D)[:, h0 * R:h1 * R].reshape(g["B"], -1)
+        out = ops.decode_attn(
+            dev(qs, dt), dev(kc["k_init"][:, :, sl], dt), dev(vc["v_init"][:, :, sl], dt),
+            dev(kc["k_local"][:, :, sl], dt), dev(vc["v_local"][:, :, sl], dt),
+            dev(kc["k_uncompressed"][:, :, nk], dt), dev(vc["v_uncompressed"][:, :, nv], dt),
+            f32(kc["k_compressed"][:, :, ck]), f32(vc["v_compressed"][:, :, cv]),
+            f32(oc.k_layer_average[0][:, ck]), f32(oc.kd_layer_average[0][:, ck]), f32(oc.k_scale[0][:, ck]),
+            f32(oc.v_layer_average[0][:, cv]), f32(oc.vd_layer_average[0][:, cv]), f32(oc.v_scale[0][:, cv]),
+            tabs, (h1 - h0) * R, h1 - h0, oc.T)
+        assert np.abs(host(out) - full[:, h0 * R:h1 * R]).max() <= 2e-6
+
+
+def test_sequence_split_merges_to_full():
+    """Disjoint slices of the middle span (one also holding sinks+window) merged by log-sum-exp."""
+    import fourierattention_b200.ops as ops
+    g = DECODE_CASES["gqa3_bf16"]
+    oc, q = _state(g)
+    dt = g["dtype"]
+    inp = decode_inputs_from_oracle(oc, dt)
+    qd = dev(q, dt)
+    full = host(ops.decode_attn(qd, num_head_q=g["Hq"], num_head_kv=g["Hkv"], T=oc.T, **inp))
+    n_mid = inp["k_mn"].shape[1]
+    cuts = [0, n_mid // 3, n_mid // 3 + 1, n_mid]
+    parts = []
+    for r in range(3):
+        loc = dict(inp)
+        loc["k_mn"] = inp["k_mn"][:, cuts[r]:cuts[r + 1]]
+        loc["v_mn"] = inp["v_mn"][:, cuts[r]:cuts[r + 1]]
+        if r != 0:
+            loc["k_sink"] = loc["v_sink"] = loc["k_win"] = loc["v_win"] = None
+        parts.append(ops.decode_attn(qd, num_head_q=g["Hq"], num_head_kv=g["Hkv"], T=oc.T, mid_l0=cuts[r],
+                                     return_lse=True, **loc))
+    rows = g["B"] * g["Hq"]
+    o = torch.stack([p[0].view(rows, -1) for p in parts])
+    m = torch.stack([p[1].view(rows) for p in parts])
+    l = torch.stack([p[2].view(rows) for p in parts])
+    merged = host(ops.merge(o, m, l)).reshape(full.shape)
+    assert np.abs(merged - full).max() <= 2e-6
+    ref = fo.merge_partials(host(m).T, host(l).T, (host(o) * host(l)[..., None]).transpose(1, 0, 2))
+    assert np.abs(host(ops.merge(o, m, l)) - ref).max() <= 2e-6
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("B,K,F,Mc,N,T,k0", [(1, 1, 16, 11, 4, 93, 40), (2, 300, 64, 41, 16, 333, 0),
+                                              (1, 2500, 96, 70, 64, 2999, 7), (2, 5000, 256, 192, 128, 5200, 0)])
+def test_compress_matches_oracle(dtype, B, K, F, Mc, N, T, k0):
+    import fourierattention_b200.ops as ops
+    rng = np.random.default_rng(K + Mc)
+    x = fo.rnd((rng.standard_normal((B, K, F)) * np.exp(rng.uniform(np.log(0.1), np.log(10), F))).astype(np.float32), dtype)
+    idx = np.sort(rng.choice(F, Mc, replace=False))
+    T_c = fo.compress_period(T)
+    c = ops.compress(dev(x, dtype), dev(idx.astype(np.int32)), N, T_c, k0)
+    ref = fo.fourier_project(x[:, :, idx], N, T_c, k0)
+    scale = max(1.0, np.abs(ref).max())
+    assert np.abs(host(c) - ref).max() <= 2e-6 * scale * max(1.0, np.sqrt(K) / 8)
+    c2 = ops.compress(dev(x, dtype), dev(idx.astype(np.int32)), N, T_c, k0, coef=c.clone(), accumulate=True)
+    assert np.abs(host(c2) - 2 * ref).max() <= 4e-6 * scale * max(1.0, np.sqrt(K) / 8)
+    strided = dev(np.concatenate([x, x], 2), dtype)[:, :, :F]
+    c3 = ops.compress(strided, dev(idx.astype(np.int32)), N, T_c, k0)
+    assert torch.equal(c3, c)
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_colstats_and_gather(dtype):
+    import fourierattention_b200.ops as ops
+    rng = np.random.default_rng(3)
+    B, K, F = 2, 1234, 80
+    x = fo.rnd(rng.standard_normal((B, K, F)).astype(np.float32) + 0.3, dtype)
+    idx = np.sort(rng.choice(F, 37, replace=False))
+    avg, dv = ops.colstats(dev(x, dtype), dev(idx.astype(np.int32)))
+    xs = x[:, :, idx].astype(np.float64)
+    a = xs.mean(1)
+    assert np.abs(host(avg) - a).max() <= 1e-6
+    assert np.abs(host(dv) - np.maximum(xs.max(1) - host(avg), host(avg) - xs.min(1))).max() <= 1e-6
+    out = torch.zeros((B, K + 2, 40), dtype=TDT[dtype], device="cuda")
+    ops.gather_cols(dev(x, dtype), dev(idx.astype(np.int32)), out[:, 1:K + 1, :37])
+    assert np.array_equal(host(out[:, 1:K + 1, :37]), x[:, :, idx])
+    assert float(out[:, 0].abs().sum()) == 0 and float(out[:, :, 37:].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("B,N,Mc,K,T", [(1, 4, 9, 30, 35), (2, 16, 70, 500, 777), (1, 128, 130, 3000, 3333)])
+def test_recon_stats_matches_oracle(B, N, Mc, K, T):
+    import fourierattention_b200.ops as ops
+    rng = np.random.default_rng(N)
+    x = rng.standard_normal((B, K, Mc))
+    coef = fo.fourier_project(x, N, fo.compress_period(T))
+    avg, dv = ops.recon_stats(dev(coef), K, T)
+    xh = fo.fourier_reconstruct(coef, K, T, faithful=False)
+    a = xh.mean(1)
+    d = np.maximum(xh.max(1) - a, a - xh.min(1))
+    assert np.abs(host(avg) - a).max() <= 2e-5 * max(1, np.abs(xh).max())
+    assert np.abs(host(dv) - d).max() <= 2e-5 * max(1, np.abs(xh).max())
+
+
+@pytest.mark.parametrize("mode", ["exact", "km57"])
+def test_evict_update_matches_oracle(mode):
+    import fourierattention_b200.ops as ops
+    rng = np.random.default_rng(9)
+    B, N, F, T = 2, 16, 48, 31995
+    kidx = np.sort(rng.choice(F, 30, replace=False)); vidx = np.sort(rng.choice(F, 17, replace=False))
+    kc = rng.standard_normal((B, 2 * N, 30)).astype(np.float32) * 50
+    vc = rng.standard_normal((B, 2 * N, 17)).astype(np.float32) * 50
+    rows = fo.rnd(rng.standard_normal((2, B, 3, F)).astype(np.float32), "bf16")
+    kd, vd = dev(kc), dev(vc)
+    buf = dev(rows, "bf16")
+    ops.evict_update(kd, buf[0][:, 1], dev(kidx.astype(np.int32)), vd, buf[1][:, 1], dev(vidx.astype(np.int32)),
+                     31741, T, ops.ANGLE_KM57 if mode == "km57" else ops.ANGLE_EXACT)
+    wk = fo.evict_update(kc, rows[0][:, 1:2][:, :, kidx], 31741, T, mode)
+    wv = fo.evict_update(vc, rows[1][:, 1:2][:, :, vidx], 31741, T, mode)
+    # cosf of the same float32 angle may differ in the last place between libraries
+    assert np.abs(host(kd) - wk).max() <= 2e-5 and np.abs(host(vd) - wv).max() <= 2e-5
+
+
+def test_errors_are_python_exceptions():
+    import fourierattention_b200.ops as ops
+    x = torch.zeros((1, 4, 8), dtype=torch.float32, device="cuda")
+    with pytest.raises(ValueError):
+        ops.colstats(x)
+    with pytest.raises(RuntimeError):
+        ops.colstats(torch.zeros((1, 4, 8), dtype=torch.float16))
+    g = DECODE_CASES["tiny"]
+    oc, q = _state(g)
+    inp = decode_inputs_from_oracle(oc, g["dtype"])
+    with pytest.raises(ValueError):      # Hq not a multiple of Hkv
+        ops.decode_attn(dev(q, g["dtype"])[:, :48], num_head_q=3, num_head_kv=2, T=oc.T, **inp)
