@@ -1000,8 +1000,10 @@ extern "C" int fa_decode_attn(const fa_decode_args_t* args, fa_stream_t stream) 
   FA_REQUIRE(a.n_sink == 0 || (a.k_sink && a.v_sink), FA_ERR_NULL, "fa_decode_attn: sink rows are null");
   FA_REQUIRE(a.n_win == 0 || (a.k_win && a.v_win), FA_ERR_NULL, "fa_decode_attn: window rows are null");
   if (a.n_mid > 0) {
-    FA_REQUIRE(a.k_coef && a.v_coef && a.avg_k_u && a.avg_k_d && a.scale_k && a.avg_v_u && a.avg_v_d && a.scale_v,
-               FA_ERR_NULL, "fa_decode_attn: coefficient or statistics pointer is null");
+    FA_REQUIRE(a.Mc_k == 0 || (a.k_coef && a.avg_k_u && a.avg_k_d && a.scale_k), FA_ERR_NULL,
+               "fa_decode_attn: K coefficient or statistics pointer is null");
+    FA_REQUIRE(a.Mc_v == 0 || (a.v_coef && a.avg_v_u && a.avg_v_d && a.scale_v), FA_ERR_NULL,
+               "fa_decode_attn: V coefficient or statistics pointer is null");
     FA_REQUIRE((a.Mn_k == 0 || a.k_mn) && (a.Mn_v == 0 || a.v_mn), FA_ERR_NULL, "fa_decode_attn: verbatim store is null");
     FA_REQUIRE(a.kc_h && a.kn_h && a.vc_h && a.vn_h && (a.Mc_k == 0 || a.kc_list) && (a.Mc_v == 0 || a.vc_list) &&
                    (a.Mn_k == 0 || a.kn_list) && (a.Mn_v == 0 || a.vn_list), FA_ERR_NULL,

@@ -214,13 +214,13 @@ def decode_attn(q, k_sink, v_sink, k_win, v_win, k_mn, v_mn, k_coef, v_coef,
         raise ValueError("K and V segments must share their batch stride")
     if a.n_mid > 0:
         for t, nm in ((k_mn, "k_mn"), (v_mn, "v_mn")):
-            if t.stride(2) != 1 or t.dtype != q.dtype:
+            if (t.shape[2] > 0 and t.stride(2) != 1) or t.dtype != q.dtype:
                 raise ValueError(f"{nm}: expected dtype {q.dtype} with a contiguous last dimension")
         for t in (k_coef, v_coef, avg_k_u, avg_k_d, scale_k, avg_v_u, avg_v_d, scale_v):
             if t.dtype != torch.float32 or not t.is_contiguous():
                 raise ValueError("coefficients and statistics must be contiguous float32")
-        a.k_mn, a.k_mn_sb, a.k_mn_sk = k_mn.data_ptr(), k_mn.stride(0), k_mn.stride(1)
-        a.v_mn, a.v_mn_sb, a.v_mn_sk = v_mn.data_ptr(), v_mn.stride(0), v_mn.stride(1)
+        a.k_mn, a.k_mn_sb, a.k_mn_sk = k_mn.data_ptr(), k_mn.stride(0), max(k_mn.stride(1), a.Mn_k)
+        a.v_mn, a.v_mn_sb, a.v_mn_sk = v_mn.data_ptr(), v_mn.stride(0), max(v_mn.stride(1), a.Mn_v)
         a.k_coef, a.v_coef = k_coef.data_ptr(), v_coef.data_ptr()
         a.avg_k_u, a.avg_k_d, a.scale_k = avg_k_u.data_ptr(), avg_k_d.data_ptr(), scale_k.data_ptr()
         a.avg_v_u, a.avg_v_d, a.scale_v = avg_v_u.data_ptr(), avg_v_d.data_ptr(), scale_v.data_ptr()
