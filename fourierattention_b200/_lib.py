@@ -10,6 +10,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libfourier_b200.so")
 
 FA_DTYPE_F16, FA_DTYPE_BF16 = 0, 1
 FA_ANGLE_EXACT, FA_ANGLE_KM57 = 0, 1
+FA_DECODE_STATIC_SCRATCH_BYTES = 24 << 20
 
 STATUS_NAMES = {0: "FA_OK", -1: "FA_ERR_NULL", -2: "FA_ERR_SHAPE", -3: "FA_ERR_DTYPE", -4: "FA_ERR_ALIGN",
                 -5: "FA_ERR_CAPACITY", -6: "FA_ERR_CUDA", -7: "FA_ERR_UNSUPPORTED"}
@@ -17,7 +18,7 @@ STATUS_NAMES = {0: "FA_OK", -1: "FA_ERR_NULL", -2: "FA_ERR_SHAPE", -3: "FA_ERR_D
 # every symbol include/fourier_b200.h declares
 EXPORTS = ["fa_version", "fa_last_error_string", "fa_gather_cols", "fa_colstats", "fa_compress_scratch_bytes",
            "fa_compress", "fa_evict_update", "fa_recon_stats_scratch_bytes", "fa_recon_stats", "fa_fourier_inverse",
-           "fa_cache_step", "fa_decode_scratch_bytes", "fa_decode_attn", "fa_merge"]
+           "fa_cache_step", "fa_decode_scratch_bytes", "fa_decode_attn", "fa_decode_attn_static", "fa_merge"]
 
 i32, i64, vp, f32, sz = C.c_int32, C.c_int64, C.c_void_p, C.c_float, C.c_size_t
 
@@ -47,12 +48,13 @@ class DecodeArgs(C.Structure):
 def _load():
     if not os.path.exists(LIB_PATH):
         raise RuntimeError(
-            f"{LIB_PATH} is missing: build it with `python -m fourierattention_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python fourierattention_b200/build.py` "
             "(nvcc, sm_100a).  This package has no fallback path.")
     lib = C.CDLL(LIB_PATH)
     for name in EXPORTS:
         if not hasattr(lib, name):
-            raise RuntimeError(f"{LIB_PATH} does not export {name}")
+            raise RuntimeError(f"{LIB_PATH} does not export {name}: it is stale, rebuild it with "
+                               "`python fourierattention_b200/build.py`")
     lib.fa_version.restype = C.c_int
     lib.fa_last_error_string.restype = C.c_char_p
     lib.fa_gather_cols.argtypes = [vp, C.c_int, C.c_int, C.c_int, i64, i64, vp, C.c_int, vp, i64, i64, vp]
@@ -72,6 +74,7 @@ def _load():
     lib.fa_decode_scratch_bytes.argtypes = [C.POINTER(DecodeArgs)]
     lib.fa_decode_scratch_bytes.restype = sz
     lib.fa_decode_attn.argtypes = [C.POINTER(DecodeArgs), vp]
+    lib.fa_decode_attn_static.argtypes = [C.POINTER(DecodeArgs), vp]
     lib.fa_merge.argtypes = [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp, vp]
     for name in EXPORTS:
         f = getattr(lib, name)

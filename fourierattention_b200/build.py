@@ -1,7 +1,9 @@
 """Builds the sm_100a shared library of this package in-tree with nvcc.
 
-    python -m fourierattention_b200.build            # build if sources are newer than the library
-    python -m fourierattention_b200.build --force
+    python fourierattention_b200/build.py            # build if sources are newer than the library
+    python fourierattention_b200/build.py --force
+
+(run it as a script: importing the package needs the library this script produces)
 
 The library (``fourierattention_b200/lib/libfourier_b200.so``) exports the C ABI declared in
 ``include/fourier_b200.h``.  It has no dependency on PyTorch.

@@ -16,6 +16,8 @@
 //   output   : merge numerators/denominators, add the compressed-V part, normalise
 #include <math.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace fa {
@@ -977,6 +979,34 @@ static int launch_decode(const DecodeParams& p, cudaStream_t st) {
   return FA_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Scratch for callers that must not allocate: a fixed array in device memory, owned by this
+// library.  Every GPU that loads the library holds these bytes until the process exits.
+// In host code the array's name is only a handle (not a device address), so the address is looked
+// up once per device with cudaGetSymbolAddress and that pointer is what the kernels receive.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[FA_DECODE_STATIC_SCRATCH_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+
+static int static_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* ptrs[MAX_DEVICES] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  FA_REQUIRE(dev >= 0 && dev < MAX_DEVICES, FA_ERR_CAPACITY, "fa_decode_attn_static: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);   // resolves against the current device
+    if (e != cudaSuccess || p == nullptr) return cuda_fail(e, "cudaGetSymbolAddress(g_static_scratch)");
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return FA_OK;
+}
+
 }  // namespace fa
 
 using namespace fa;
@@ -1033,4 +1063,24 @@ extern "C" int fa_merge(const float* o, const float* m, const float* l, int n_pa
   merge_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(o, m, l, n_parts, rows, D, out);
   FA_CHECK_LAUNCH("fa_merge");
   return FA_OK;
+}
+
+extern "C" int fa_decode_attn_static(const fa_decode_args_t* args, fa_stream_t stream) {
+  FA_REQUIRE(args, FA_ERR_NULL, "fa_decode_attn_static: null argument block");
+  fa_decode_args_t a = *args;
+  a.scratch = nullptr;
+  a.scratch_bytes = 0;
+  DecodeParams p;
+  int rc = make_plan(a, p);
+  if (rc != FA_OK) return rc;
+  const size_t need = (size_t)p.scratch_floats * sizeof(float);
+  FA_REQUIRE(need <= (size_t)FA_DECODE_STATIC_SCRATCH_BYTES, FA_ERR_CAPACITY,
+             "fa_decode_attn_static: this problem needs %zu bytes of scratch, the built-in buffer holds %zu; "
+             "use fa_decode_attn with caller-provided scratch", need, (size_t)FA_DECODE_STATIC_SCRATCH_BYTES);
+  void* ptr = nullptr;
+  rc = static_scratch_address(&ptr);
+  if (rc != FA_OK) return rc;
+  a.scratch = ptr;
+  a.scratch_bytes = (size_t)FA_DECODE_STATIC_SCRATCH_BYTES;
+  return fa_decode_attn(&a, stream);
 }

@@ -172,10 +172,13 @@ class DecodeTables:
 
 def decode_attn(q, k_sink, v_sink, k_win, v_win, k_mn, v_mn, k_coef, v_coef,
                 avg_k_u, avg_k_d, scale_k, avg_v_u, avg_v_d, scale_v, tables,
-                num_head_q, num_head_kv, T, sm_scale=-1.0, mid_l0=0, out=None, return_lse=False, phase_events=None):
+                num_head_q, num_head_kv, T, sm_scale=-1.0, mid_l0=0, out=None, return_lse=False, phase_events=None,
+                static_scratch=False):
     """Fused decode attention.  q: (B, Hq*D) (or (B,1,Hq*D)); sinks/window: (B, n, F) or None;
     k_mn/v_mn: (B, n_mid, Mn) row-strided views; coefficients (B, 2N, Mc) float32; statistics
-    (B, Mc) float32.  Returns (B, Hq, D) float32 (plus (m, l) if ``return_lse``)."""
+    (B, Mc) float32.  Returns (B, Hq, D) float32 (plus (m, l) if ``return_lse``).
+    ``static_scratch=True`` goes through ``fa_decode_attn_static``: no scratch tensor is taken from
+    PyTorch's allocator, the kernels use the fixed buffer inside the library (see fourier_b200.h)."""
     _need_cuda(q)
     if q.dim() == 3:
         q = q[:, 0]
@@ -240,6 +243,11 @@ def decode_attn(q, k_sink, v_sink, k_win, v_win, k_mn, v_mn, k_coef, v_coef,
     if phase_events is not None:       # five torch.cuda.Event(enable_timing=True), see fourier_b200.h
         ev = (C.c_void_p * 5)(*[e.cuda_event for e in phase_events])
         a.phase_events_host = C.cast(ev, C.c_void_p)
+    if static_scratch:
+        with torch.cuda.device(dev):
+            check(lib.fa_decode_attn_static(C.byref(a), _stream(q)), "fa_decode_attn_static")
+        _count(4 if a.n_mid > 0 else 2)
+        return (out, m, l) if return_lse else out
     with torch.cuda.device(dev):
         nbytes = lib.fa_decode_scratch_bytes(C.byref(a))
         if nbytes == 0:

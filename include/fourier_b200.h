@@ -164,6 +164,29 @@ typedef struct {
 size_t fa_decode_scratch_bytes(const fa_decode_args_t* args_host);
 int fa_decode_attn(const fa_decode_args_t* args_host, fa_stream_t stream);
 
+/* The same attention for hosts that cannot allocate device memory around the call.
+ *
+ * This entry point has no counterpart in the reference.  It exists for callers such as inference
+ * servers that hand the whole HBM heap to their own page allocator at start-up, or code running where a
+ * cudaMalloc (and the device-wide synchronisation it implies) is not allowed: they have nowhere to get
+ * the scratch buffer fa_decode_attn asks for.  Here the scratch is a fixed array of
+ * FA_DECODE_STATIC_SCRATCH_BYTES inside the library's own device image; args->scratch and
+ * args->scratch_bytes are ignored, inputs and outputs are still the caller's.
+ *
+ *  - The call makes no cudaMalloc / cudaFree and uses no allocating library routine.
+ *  - A problem whose plan needs more scratch than the array holds is refused with FA_ERR_CAPACITY
+ *    (fa_decode_scratch_bytes() tells the need); the Llama-3.1-8B / 32k / batch-8 layer call needs
+ *    18.4 MiB, a single 512k-token sequence with M = 1024 needs 33.6 MiB and is refused.
+ *  - Every GPU that loads the library reserves the array until the process ends.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *    device current).  Make that first call outside any stream capture.
+ *  - All calls on a device share the one array and it keeps whatever the last call left there.  Nothing
+ *    has to be cleared between calls: every word a call reads was written earlier in that same call.  Two
+ *    calls that overlap on the GPU (different streams, or graphs replayed concurrently) race on it; keep
+ *    calls of this entry point ordered on one stream per device. */
+#define FA_DECODE_STATIC_SCRATCH_BYTES (24u << 20)
+int fa_decode_attn_static(const fa_decode_args_t* args_host, fa_stream_t stream);
+
 /* Log-sum-exp merge of n_parts partial results (KM:756-776), e.g. one per device of a
  * sequence split:  out = sum_i o_i l_i 2^(m_i - m*) / sum_i l_i 2^(m_i - m*),
  * with o_i the NORMALISED partial outputs (rows, D), m_i/l_i (rows).  parts are stacked:

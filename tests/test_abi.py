@@ -16,8 +16,8 @@ HEADER = os.path.join(ROOT, "include", "fourier_b200.h")
 @pytest.fixture(scope="module")
 def L():
     sys.path.insert(0, ROOT)
-    from fourierattention_b200 import build
-    build.build()
+    import __graft_entry__
+    __graft_entry__._load_builder().build()
     from fourierattention_b200 import _lib
     return _lib
 
