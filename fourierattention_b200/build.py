@@ -38,7 +38,7 @@ def _stale(target, deps):
 
 def build(force=False, verbose=False):
     os.makedirs(LIB_DIR, exist_ok=True)
-    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h", ".inc"))]
     headers.append(os.path.join(ROOT, "include", "fourier_b200.h"))
     objs = []
     procs = []

@@ -20,7 +20,7 @@ import torch
 
 from . import ops
 
-__all__ = ["Cache", "DynamicCache", "StaticCache", "compress_period"]
+__all__ = ["Cache", "DynamicCache", "StaticCache", "compress_period", "shard_tables", "span_slice"]
 
 
 def compress_period(T: int) -> int:
@@ -56,6 +56,29 @@ class StaticCache(Cache):
 
 def _round8(x):
     return (x + 7) // 8 * 8
+
+
+def shard_tables(ent, h0, h1):
+    """Restrict one layer's ``_splithead`` entry to KV heads h0..h1-1 and rebase the flat dims, so that a
+    rank owning those heads can run the path on its slice alone (every quantity on the path is per KV
+    head: cache_utils_fourier.py:444-452 keeps cumulative per-head offsets for exactly this lookup)."""
+    n_heads = len(ent["kc_h_list"])
+    F = len(ent["kc_list"]) + len(ent["kn_list"])
+    D = F // n_heads
+    out = {}
+    for t in ("kc", "kn", "vc", "vn"):
+        cum = [0] + list(ent[f"{t}_h_list"])
+        lst = ent[f"{t}_list"][cum[h0]:cum[h1]]
+        out[f"{t}_list"] = [int(i) - h0 * D for i in lst]
+        out[f"{t}_h_list"] = [cum[h] - cum[h0] for h in range(h0 + 1, h1 + 1)]
+    return out
+
+
+def span_slice(n_rows, rank, world):
+    """Rows [lo, hi) of a middle span of ``n_rows`` rows that rank ``rank`` of ``world`` keeps when the span
+    is split by sequence (equal contiguous slices, the last one may be shorter)."""
+    per = (n_rows + world - 1) // world
+    return min(n_rows, rank * per), min(n_rows, (rank + 1) * per)
 
 
 class _LayerState:
@@ -139,20 +162,9 @@ class DynamicCache(Cache):
 
     # ------------------------------------------------------------------------------------------
     def _shard_tables(self, ent):
-        """Restrict a layer's tables to this rank's KV heads and rebase the flat dims."""
         if self.kv_head_range is None:
             return ent
-        h0, h1 = self.kv_head_range
-        n_heads = len(ent["kc_h_list"])
-        F = len(ent["kc_list"]) + len(ent["kn_list"])
-        D = F // n_heads
-        out = {}
-        for t in ("kc", "kn", "vc", "vn"):
-            cum = [0] + list(ent[f"{t}_h_list"])
-            lst = ent[f"{t}_list"][cum[h0]:cum[h1]]
-            out[f"{t}_list"] = [int(i) - h0 * D for i in lst]
-            out[f"{t}_h_list"] = [cum[h] - cum[h0] for h in range(h0 + 1, h1 + 1)]
-        return out
+        return shard_tables(ent, *self.kv_head_range)
 
     def __len__(self):
         return len(self.key_cache)
@@ -207,9 +219,7 @@ class DynamicCache(Cache):
     def _span_slice(self, n_rows):
         if self.seq_shard is None:
             return 0, n_rows
-        r, w = self.seq_shard
-        per = (n_rows + w - 1) // w
-        return min(n_rows, r * per), min(n_rows, (r + 1) * per)
+        return span_slice(n_rows, *self.seq_shard)
 
     def _prefill_layer(self, key_states, value_states, layer_idx):
         B, P, F = key_states.shape

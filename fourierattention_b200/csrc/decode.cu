@@ -14,9 +14,12 @@
 //              (max, denominator, verbatim-V numerator, g)      (reads every cache row once)
 //   contract : merge g over chunks, contract with C_v           (reads C_v once)
 //   output   : merge numerators/denominators, add the compressed-V part, normalise
+#include <cuda.h>
 #include <math.h>
+#include <stdlib.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -30,6 +33,10 @@ constexpr int IT_IL = 2;        // 4-dim groups per thread in the sinks+window P
 constexpr float NEG_BIG = -1.0e30f;
 
 struct DecodeParams {
+  // tensor maps of the verbatim stores (tensor-core pass only): (column, row, sequence) tiles of
+  // 64 x 64 elements, 128-byte swizzle, out-of-range rows and columns read as zero
+  alignas(64) CUtensorMap tm_k;
+  alignas(64) CUtensorMap tm_v;
   fa_decode_args_t a;
   int R, F, n_il;
   float c2;  // sm_scale * log2(e)
@@ -39,8 +46,11 @@ struct DecodeParams {
   int n_rb, rb_rows;
   int pitchK, pitchV, qpitch;
   int smem_main, smem_prepare, smem_contract;
+  int force_exact;     // debugging / testing aid: never pick the tensor-core pass
+  int fast, fNT, fNH;  // tensor-core middle-span pass: column tiles of 8 heads, halves per super-tile
   // scratch
   float *w, *cst, *m_part, *l_part, *o_part, *g_part, *cv_part;
+  int* err;  // set by a kernel whose bounded wait gave up; the output kernel then poisons the result
   int64_t scratch_floats;
 };
 
@@ -134,6 +144,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_prepare_kernel(const __gri
       }
     }
   }
+  if (blockIdx.x == 0 && b == 0 && tid == 0) *p.err = 0;
   if (blockIdx.x == 0) {
     for (int h = warp; h < a.Hq; h += DEC_THREADS / 32) {
       const int g = h / R;
@@ -148,6 +159,9 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_prepare_kernel(const __gri
     }
   }
 }
+
+// barrier of the 256 threads of a CTA
+__device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, 256;\n" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------
 // main, part 1: sinks + window rows (dense K/V rows, all heads of the rank)
@@ -216,7 +230,7 @@ __device__ void il_chunk(const DecodeParams& p, int b, int chunk, unsigned char*
     const int row0 = r0 + t * TR;
     const int valid = min(TR, r1 - row0);
     cp_async_wait<1>();
-    __syncthreads();
+    compute_sync();
     // ---- scores -------------------------------------------------------------------------
     for (int it = tid; it < TR * Hkv; it += DEC_THREADS) {
       const int row = it % TR, g = it / TR;
@@ -242,7 +256,7 @@ __device__ void il_chunk(const DecodeParams& p, int b, int chunk, unsigned char*
       for (int r = 0; r < R_MAX; ++r)
         if (r < R) S[row * Hqp + g * R + r] = acc[r];
     }
-    __syncthreads();
+    compute_sync();
     if (t + 1 < nt) il_issue_tile<T>(p, b, a.k_sink, a.k_win, row0 + TR, r1, ks, TR, F, tid);
     cp_async_commit();
     // ---- online softmax, one warp per head ----------------------------------------------
@@ -267,7 +281,7 @@ __device__ void il_chunk(const DecodeParams& p, int b, int chunk, unsigned char*
       }
     }
     cp_async_wait<1>();
-    __syncthreads();
+    compute_sync();
     // ---- PV -----------------------------------------------------------------------------
 #pragma unroll
     for (int i = 0; i < IT_IL; ++i) {
@@ -300,7 +314,7 @@ __device__ void il_chunk(const DecodeParams& p, int b, int chunk, unsigned char*
         }
       }
     }
-    __syncthreads();
+    compute_sync();
     if (t + 1 < nt) il_issue_tile<T>(p, b, a.v_sink, a.v_win, row0 + TR, r1, vs, TR, F, tid);
     cp_async_commit();
   }
@@ -680,6 +694,21 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) decode_main_kernel(const __gri
   }
 }
 
+#include "decode_fast.cuh"
+
+constexpr int FAST_THREADS = DEC_THREADS;
+
+template <typename T, int NT, int NH>
+__global__ void __launch_bounds__(FAST_THREADS, 1) decode_main_fast_kernel(const __grid_constant__ DecodeParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const int b = blockIdx.y;
+  if ((int)blockIdx.x < p.n_il_chunks) {
+    il_chunk<T>(p, b, blockIdx.x, smem_raw);
+  } else {
+    mid_chunk_fast<T, NT, NH>(p, b, blockIdx.x - p.n_il_chunks, smem_raw);
+  }
+}
+
 // merge weights of every chunk slot for head h:  a_i = 2^(m_i - m*)  (0 for an empty slot)
 __device__ __forceinline__ float slot_max(const DecodeParams& p, int b, int h) {
   float ms = NEG_BIG;
@@ -803,7 +832,9 @@ __global__ void __launch_bounds__(128) decode_output_kernel(const __grid_constan
     }
   }
   __syncthreads();
-  const float inv = 1.0f / L;
+  // a kernel of this call gave up a bounded wait: make the failure visible instead of returning numbers
+  const bool poisoned = (a.n_mid > 0) && (*p.err != 0);
+  const float inv = poisoned ? __int_as_float(0x7fc00000) : 1.0f / L;
   for (int d = tid; d < D; d += blockDim.x) a.out[((int64_t)b * Hq + h) * D + d] = O[d] * inv;
   if (tid == 0) {
     if (a.m_out) a.m_out[(int64_t)b * Hq + h] = s_ms;
@@ -838,6 +869,39 @@ __global__ void merge_kernel(const float* __restrict__ o, const float* __restric
 // ---------------------------------------------------------------------------------------------
 constexpr int SMEM_LIMIT = 200 * 1024;
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(f);
+  });
+  return fn;
+}
+
+// (cols x rows x B) view of a verbatim store with 64 x 64 boxes
+static int make_store_map(CUtensorMap* m, const void* base, int dtype, int cols, int rows, int64_t row_stride,
+                          int B, int64_t batch_stride) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  FA_REQUIRE(enc != nullptr, FA_ERR_CUDA, "fa_decode_attn: cuTensorMapEncodeTiled is not available");
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)B};
+  cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)(B > 1 ? batch_stride : row_stride * rows) * 2};
+  cuuint32_t box[3] = {64, 64, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, dtype == FA_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  FA_REQUIRE(r == CUDA_SUCCESS, FA_ERR_CUDA, "fa_decode_attn: cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return FA_OK;
+}
+
 static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
   FA_REQUIRE(a.B > 0 && a.Hq > 0 && a.Hkv > 0 && a.D > 0, FA_ERR_SHAPE, "fa_decode_attn: B, Hq, Hkv, D must be positive");
   FA_REQUIRE(a.Hq % a.Hkv == 0, FA_ERR_SHAPE, "fa_decode_attn: Hq (%d) must be a multiple of Hkv (%d)", a.Hq, a.Hkv);
@@ -846,6 +910,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
              "fa_decode_attn: no keys to attend");
   FA_REQUIRE(a.D % 8 == 0, FA_ERR_ALIGN, "fa_decode_attn: head_dim (%d) must be a multiple of 8", a.D);
   p.a = a;
+  p.force_exact = (getenv("FA_DECODE_EXACT") != nullptr);
   p.R = a.Hq / a.Hkv;
   FA_REQUIRE(p.R <= R_MAX, FA_ERR_CAPACITY, "fa_decode_attn: at most %d query heads per KV head (got %d)", R_MAX, p.R);
   p.F = a.Hkv * a.D;
@@ -896,8 +961,32 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
     }
     FA_REQUIRE(ok, FA_ERR_UNSUPPORTED, "fa_decode_attn: no head grouping fits shared memory (N=%d, R=%d, D=%d)", a.N,
                p.R, a.D);
+    // tensor-core pass: usable when the spectral score turns by at most 1.5 cycles over a 128- or
+    // 64-token super-tile (interpolation through 16 nodes is then exact to ~1e-7) and the shape fits
+    // its register / shared-memory tiling; otherwise the exact CUDA-core pass above is used
+    p.fast = 0;
+    {
+      const int NT = ceil_div(a.Hq, 8);
+      auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+      const bool shape_ok = a.N % 8 == 0 && a.N <= 256 && NT <= FNT_MAX && a.Mn_k <= 256 && a.Mn_v <= 256;
+      const bool align_ok = (a.Mn_k == 0 || (al16(a.k_mn) && a.k_mn_sk % 8 == 0 && a.k_mn_sb % 8 == 0)) &&
+                            (a.Mn_v == 0 || (al16(a.v_mn) && a.v_mn_sk % 8 == 0 && a.v_mn_sb % 8 == 0));
+      int NH = 0;
+      if ((int64_t)128 * (a.N - 1) * 2 <= (int64_t)3 * a.T) NH = 2;
+      else if ((int64_t)64 * (a.N - 1) * 2 <= (int64_t)3 * a.T) NH = 1;
+      if (shape_ok && align_ok && NH > 0 && !p.force_exact) {
+        const FastSmem L = fast_smem(a.N, NT, NH, a.Mn_k, a.Mn_v, a.dtype == FA_DTYPE_BF16);
+        if (L.total <= 227 * 1024) {
+          p.fast = 1; p.fNT = NT; p.fNH = NH;
+          p.n_groups = 1; p.kvh = a.Hkv; p.HG = a.Hq;
+          J = FH * NH;
+          p.J = J;
+          mid_smem_bytes = L.total;
+        }
+      }
+    }
     const int sms = sm_count();
-    int target = (3 * sms) / (a.B * p.n_groups) - p.n_il_chunks;
+    int target = ((p.fast ? 1 : 3) * sms) / (a.B * p.n_groups) - p.n_il_chunks;
     const int max_chunks = ceil_div(a.n_mid, J);
     if (target < 1) target = 1;
     if (target > max_chunks) target = max_chunks;
@@ -928,10 +1017,12 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
   const int64_t ow = take(B * Hq * 2 * a.N), oc = take(B * Hq), om = take(B * p.NCH * Hq), ol = take(B * p.NCH * Hq);
   const int64_t oo = take(B * p.NCH * Hq * a.D), og = take(B * p.n_mid_chunks * Hq * 2 * a.N);
   const int64_t ov = take(B * p.n_rb * p.R * a.Mc_v);
+  const int64_t oe = take(4);
   p.scratch_floats = o;
   float* s = reinterpret_cast<float*>(a.scratch);
   p.w = s + ow; p.cst = s + oc; p.m_part = s + om; p.l_part = s + ol; p.o_part = s + oo; p.g_part = s + og;
   p.cv_part = s + ov;
+  p.err = reinterpret_cast<int*>(s + oe);
   return FA_OK;
 }
 
@@ -959,9 +1050,20 @@ static int launch_decode(const DecodeParams& p, cudaStream_t st) {
     FA_CHECK_LAUNCH("fa_decode_attn(prepare)");
   }
   mark(1);
-  if ((rc = set_smem(decode_main_kernel<T>, p.smem_main)) != FA_OK) return rc;
   dim3 g2(p.n_il_chunks + p.n_mid_chunks * p.n_groups, a.B);
-  decode_main_kernel<T><<<g2, DEC_THREADS, p.smem_main, st>>>(p);
+  if (p.fast) {
+#define FA_FAST_CASE(NT_, NH_)                                                                   \
+  if (p.fNT == NT_ && p.fNH == NH_) {                                                            \
+    if ((rc = set_smem(decode_main_fast_kernel<T, NT_, NH_>, p.smem_main)) != FA_OK) return rc;  \
+    decode_main_fast_kernel<T, NT_, NH_><<<g2, FAST_THREADS, p.smem_main, st>>>(p);               \
+  }
+    FA_FAST_CASE(1, 1) FA_FAST_CASE(2, 1) FA_FAST_CASE(3, 1) FA_FAST_CASE(4, 1)
+    FA_FAST_CASE(1, 2) FA_FAST_CASE(2, 2) FA_FAST_CASE(3, 2) FA_FAST_CASE(4, 2)
+#undef FA_FAST_CASE
+  } else {
+    if ((rc = set_smem(decode_main_kernel<T>, p.smem_main)) != FA_OK) return rc;
+    decode_main_kernel<T><<<g2, DEC_THREADS, p.smem_main, st>>>(p);
+  }
   FA_CHECK_LAUNCH("fa_decode_attn(main)");
   mark(2);
   if (a.n_mid > 0) {
@@ -1020,6 +1122,16 @@ extern "C" size_t fa_decode_scratch_bytes(const fa_decode_args_t* args) {
   return (size_t)p.scratch_floats * sizeof(float);
 }
 
+extern "C" int fa_decode_path(const fa_decode_args_t* args) {
+  FA_REQUIRE(args, FA_ERR_NULL, "fa_decode_path: null argument block");
+  DecodeParams p;
+  fa_decode_args_t a = *args;
+  a.scratch = nullptr;
+  int rc = make_plan(a, p);
+  if (rc != FA_OK) return rc;
+  return (a.n_mid > 0 && p.fast) ? 1 : 0;
+}
+
 extern "C" int fa_decode_attn(const fa_decode_args_t* args, fa_stream_t stream) {
   FA_REQUIRE(args, FA_ERR_NULL, "fa_decode_attn: null argument block");
   const fa_decode_args_t& a = *args;
@@ -1052,6 +1164,12 @@ extern "C" int fa_decode_attn(const fa_decode_args_t* args, fa_stream_t stream) 
     FA_REQUIRE(al16(a.k_win) && al16(a.v_win) && a.win_sb % 8 == 0, FA_ERR_ALIGN,
                "fa_decode_attn: window rows must be 16-byte aligned");
   FA_REQUIRE(a.q_sb % 8 == 0 || a.B == 1, FA_ERR_ALIGN, "fa_decode_attn: q batch stride must be a multiple of 8");
+  if (p.fast) {
+    if (a.Mn_k > 0 && (rc = make_store_map(&p.tm_k, a.k_mn, a.dtype, a.Mn_k, a.n_mid, a.k_mn_sk, a.B, a.k_mn_sb)) != FA_OK)
+      return rc;
+    if (a.Mn_v > 0 && (rc = make_store_map(&p.tm_v, a.v_mn, a.dtype, a.Mn_v, a.n_mid, a.v_mn_sk, a.B, a.v_mn_sb)) != FA_OK)
+      return rc;
+  }
   cudaStream_t st = (cudaStream_t)stream;
   return a.dtype == FA_DTYPE_F16 ? launch_decode<__half>(p, st) : launch_decode<__nv_bfloat16>(p, st);
 }
@@ -1084,3 +1202,17 @@ extern "C" int fa_decode_attn_static(const fa_decode_args_t* args, fa_stream_t s
   a.scratch_bytes = (size_t)FA_DECODE_STATIC_SCRATCH_BYTES;
   return fa_decode_attn(&a, stream);
 }
+
+#ifdef FA_PHASE_TIMING
+// debugging aid (only in builds with -DFA_PHASE_TIMING): cumulative clock ticks per phase of the
+// tensor-core middle-span pass, thread 0 of every CTA
+extern "C" int fa_debug_phase_clocks(unsigned long long* out16_host, int reset) {
+  cudaDeviceSynchronize();
+  if (out16_host) cudaMemcpyFromSymbol(out16_host, fa::g_phase_clk, sizeof(unsigned long long) * 16);
+  if (reset) {
+    unsigned long long z[16] = {0};
+    cudaMemcpyToSymbol(fa::g_phase_clk, z, sizeof(z));
+  }
+  return 0;
+}
+#endif

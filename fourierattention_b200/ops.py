@@ -15,6 +15,7 @@ ANGLE_EXACT, ANGLE_KM57 = _lib.FA_ANGLE_EXACT, _lib.FA_ANGLE_KM57
 
 _scratch = {}
 launch_count = 0          # kernels-launching C-ABI calls made so far (for benchmark accounting)
+last_decode_path = None   # fa_decode_path() of the most recent decode_attn call (1 = tensor-core pass)
 
 
 def _dt(t):
@@ -243,6 +244,8 @@ def decode_attn(q, k_sink, v_sink, k_win, v_win, k_mn, v_mn, k_coef, v_coef,
     if phase_events is not None:       # five torch.cuda.Event(enable_timing=True), see fourier_b200.h
         ev = (C.c_void_p * 5)(*[e.cuda_event for e in phase_events])
         a.phase_events_host = C.cast(ev, C.c_void_p)
+    global last_decode_path
+    last_decode_path = lib.fa_decode_path(C.byref(a))
     if static_scratch:
         with torch.cuda.device(dev):
             check(lib.fa_decode_attn_static(C.byref(a), _stream(q)), "fa_decode_attn_static")

@@ -162,6 +162,12 @@ typedef struct {
 
 /* Bytes of scratch fa_decode_attn needs for this geometry (only the size fields are read). */
 size_t fa_decode_scratch_bytes(const fa_decode_args_t* args_host);
+/* Which middle-span pass fa_decode_attn will run for these arguments (sizes, strides and pointer
+ * alignment are read): 1 = tensor-core pass (the spectral score is evaluated at 16 nodes per 64/128-token
+ * super-tile and interpolated; needs N % 8 == 0, N <= 256, Hq <= 32, Mn_* <= 256, 16-byte aligned verbatim
+ * rows and at most 1.5 turns of the highest frequency per super-tile), 0 = exact CUDA-core pass,
+ * negative = fa_status_t.  Setting the environment variable FA_DECODE_EXACT forces 0. */
+int fa_decode_path(const fa_decode_args_t* args_host);
 int fa_decode_attn(const fa_decode_args_t* args_host, fa_stream_t stream);
 
 /* The same attention for hosts that cannot allocate device memory around the call.

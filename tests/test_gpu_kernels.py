@@ -33,6 +33,42 @@ DECODE_CASES = {
 }
 
 
+# shapes whose period is long enough for the tensor-core pass (<= 1.5 turns of the top frequency per
+# 128- or 64-token super-tile)
+FAST_CASES = {
+    "fast_gqa4_bf16": _geom(B=2, Hq=8, Hkv=2, D=64, S=4, W=17, M=16, P=700, dtype="bf16", ncomp=40, seed=201),
+    "fast_32heads_fp16": _geom(B=1, Hq=32, Hkv=8, D=128, S=4, W=64, M=32, P=1500, ncomp=96, seed=202),
+    "fast_gqa3_half_tiles": _geom(B=2, Hq=24, Hkv=8, D=128, S=4, W=32, M=64, P=1500, dtype="bf16", ncomp=80, seed=203),
+    "fast_ragged": _geom(B=2, Hq=8, Hkv=4, D=32, S=2, W=9, M=16, P=901, ragged=True, seed=204),
+    "fast_one_kv_head": _geom(B=3, Hq=4, Hkv=1, D=128, S=4, W=33, M=16, P=777, ncomp=96, seed=205),
+    "fast_nothing_verbatim": _geom(B=1, Hq=4, Hkv=2, D=16, W=6, M=16, P=800, ncomp=16, seed=206),
+    "fast_nothing_compressed": _geom(B=1, Hq=4, Hkv=2, D=16, W=6, M=16, P=800, ncomp=0, seed=207),
+    "fast_llama8b_layer": _geom(B=1, Hq=32, Hkv=8, D=128, S=4, W=128, M=512, P=24000, dtype="bf16", ncomp=96, seed=208),
+}
+
+
+@pytest.mark.parametrize("name", list(FAST_CASES))
+def test_decode_attn_tensor_core_pass(name, monkeypatch):
+    import fourierattention_b200.ops as ops
+    g = FAST_CASES[name]
+    oc, q = _state(g)
+    inp = decode_inputs_from_oracle(oc, g["dtype"])
+    qd = dev(q, g["dtype"])
+    out = ops.decode_attn(qd, num_head_q=g["Hq"], num_head_kv=g["Hkv"], T=oc.T, **inp)
+    assert ops.last_decode_path == 1, "shape was expected to take the tensor-core pass"
+    ideal = oc.attend(q, 0, g["Hq"], g["Hkv"], faithful=False)[:, :, 0]
+    err = np.abs(host(out) - ideal).max()
+    # this pass rounds the probabilities to float16 before PV (as the reference's flash-attention does);
+    # everything else is carried to ~2^-22
+    assert err <= 1.5e-4 * max(1.0, np.abs(ideal).max()), err
+    ref = oc.attend(q, 0, g["Hq"], g["Hkv"], faithful=True)[:, :, 0]
+    assert attn_err_excess(host(out), ref, g["dtype"]) <= 0
+    monkeypatch.setenv("FA_DECODE_EXACT", "1")
+    exact = ops.decode_attn(qd, num_head_q=g["Hq"], num_head_kv=g["Hkv"], T=oc.T, **inp)
+    assert ops.last_decode_path == 0
+    assert np.abs(host(exact) - ideal).max() <= 3e-5 * max(1.0, np.abs(ideal).max())
+
+
 def _state(g):
     tables, k, v, qs = case_inputs(g)
     oc = oracle_cache(g, tables)
