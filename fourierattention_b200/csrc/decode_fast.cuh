@@ -186,10 +186,10 @@ __host__ __device__ inline FastSmem fast_smem(int N, int NT, int NH, int Mn_k, i
   s.qpitch = mnk16 + 8;
   s.qn = take(HN * s.qpitch * 2);
   s.smax = take(4 * HN * 4);
-  s.ssum = take(4 * HN * 4);
+  s.ssum = take(4 * HN * 4);   // running denominators, one row per 16-token slice of a half tile
   s.alpha = take(HN * 4);
   s.alpha_prod = take(HN * 4);
-  s.m_run = take(HN * 4);
+  s.m_run = take(2 * HN * 4);  // running maxima, ping-pong between consecutive half tiles
   s.l_run = take(HN * 4);
   s.cst = take(HN * 4);
   s.kcol = take(2 * FNT_MAX * 4);
@@ -291,15 +291,20 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
       const int lf = l0 + (i >> 1) * FH;   // K and V half tiles alternate, 64 tokens each
       const bool is_v = (i & 1) != 0;
       const int nb = is_v ? nbV : nbK;
-      if (lane == 0) {
-        mbar_expect_tx(bars + issue_slot, (uint32_t)nb * 8192u);
+      if (lane == 0) mbar_expect_tx(bars + issue_slot, (uint32_t)nb * 8192u);
+      __syncwarp();
+      if (lane < nb) {   // one box per lane, so the copies are issued side by side
         unsigned char* dst = reinterpret_cast<unsigned char*>(slots) + issue_slot * L.slot_bytes;
-        for (int bx = 0; bx < nb; ++bx) tma_box(dst + bx * 8192, is_v ? &p.tm_v : &p.tm_k, 64 * bx, lf, b, bars + issue_slot);
+        tma_box(dst + lane * 8192, is_v ? &p.tm_v : &p.tm_k, 64 * lane, lf, b, bars + issue_slot);
       }
       issue_slot = (issue_slot == 2) ? 0 : issue_slot + 1;
       ++issued;
     }
   };
+  if (tid == 7 * 32) {
+    if (nbK) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&p.tm_k) : "memory");
+    if (nbV) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&p.tm_v) : "memory");
+  }
   issue_upto(3);
 
   for (int e = tid; e < FD * N; e += DEC_THREADS) {
@@ -341,7 +346,9 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
     alpha[h] = 1.f;
     alpha_prod[h] = 1.f;
     m_run[h] = NEG_BIG;
+    m_run[HN + h] = NEG_BIG;
     l_run[h] = 0.f;
+    for (int r = 0; r < 4; ++r) ssum[r * HN + h] = 0.f;
     cst[h] = (h < Hq) ? p.cst[(int64_t)b * Hq + h] : 0.f;
   }
   if (tid < NT) {
@@ -415,6 +422,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
   consumer_sync();
 
   FA_TICK(0);
+  int mbuf = 0;            // which copy of m_run holds the current maxima
   int use_slot = 0;        // ring slot of the next half tile to consume
   uint32_t use_round = 0;  // how many times the ring has wrapped
   for (int st = 0; st < nst; ++st) {
@@ -580,7 +588,8 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
         const int nt = ntp + 2 * i;
         if (nt < NT) {
           const int col = 8 * nt + 2 * tq;
-          float mn0 = m_run[col], mn1 = m_run[col + 1];
+          const float mo0 = m_run[mbuf * HN + col], mo1 = m_run[mbuf * HN + col + 1];
+          float mn0 = mo0, mn1 = mo1;
 #pragma unroll
           for (int r = 0; r < 4; ++r) {
             mn0 = fmaxf(mn0, smax[r * HN + col]);
@@ -617,26 +626,23 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
             s1 += __shfl_xor_sync(0xffffffffu, s1, o);
           }
           if (gq == 0) {
-            ssum[mt4 * HN + col] = s0;
-            ssum[mt4 * HN + col + 1] = s1;
+            // one lane owns (16-token slice, column): its denominator is rescaled and extended here,
+            // the four slices are added when the chunk is finished
+            const float al0 = exp2f(mo0 - mn0), al1 = exp2f(mo1 - mn1);
+            ssum[mt4 * HN + col] = ssum[mt4 * HN + col] * al0 + s0;
+            ssum[mt4 * HN + col + 1] = ssum[mt4 * HN + col + 1] * al1 + s1;
+            if (mt4 == 0) {
+              alpha[col] = al0;
+              alpha[col + 1] = al1;
+              alpha_prod[col] *= al0;
+              alpha_prod[col + 1] *= al1;
+              m_run[(mbuf ^ 1) * HN + col] = mn0;
+              m_run[(mbuf ^ 1) * HN + col + 1] = mn1;
+            }
           }
         }
       }
-      consumer_sync();
-      if (tid < HN) {
-        const float m_old = m_run[tid];
-        float mn = m_old, sm = 0.f;
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          mn = fmaxf(mn, smax[r * HN + tid]);
-          sm += ssum[r * HN + tid];
-        }
-        const float al = exp2f(m_old - mn);
-        alpha[tid] = al;
-        alpha_prod[tid] *= al;
-        l_run[tid] = l_run[tid] * al + sm;
-        m_run[tid] = mn;
-      }
+      mbuf ^= 1;
       consumer_sync();
       FA_TICK(6);
       // ---- F: project the probabilities onto the nodes (warps 0..NT-1, one column tile each) -----
@@ -753,8 +759,8 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
   // ---- chunk partials ---------------------------------------------------------------------------
   const int64_t slot = (int64_t)b * p.NCH + p.n_il_chunks + chunk;
   for (int h = tid; h < Hq; h += DEC_THREADS) {
-    p.m_part[slot * Hq + h] = m_run[h];
-    p.l_part[slot * Hq + h] = l_run[h];
+    p.m_part[slot * Hq + h] = m_run[mbuf * HN + h];
+    p.l_part[slot * Hq + h] = (ssum[h] + ssum[HN + h]) + (ssum[2 * HN + h] + ssum[3 * HN + h]);
   }
   float* ob = p.o_part + slot * Hq * D;
   for (int e = tid; e < Hq * D; e += DEC_THREADS) ob[e] = 0.f;

@@ -38,7 +38,7 @@ DECODE_CASES = {
 FAST_CASES = {
     "fast_gqa4_bf16": _geom(B=2, Hq=8, Hkv=2, D=64, S=4, W=17, M=16, P=700, dtype="bf16", ncomp=40, seed=201),
     "fast_32heads_fp16": _geom(B=1, Hq=32, Hkv=8, D=128, S=4, W=64, M=32, P=1500, ncomp=96, seed=202),
-    "fast_gqa3_half_tiles": _geom(B=2, Hq=24, Hkv=8, D=128, S=4, W=32, M=64, P=1500, dtype="bf16", ncomp=80, seed=203),
+    "fast_gqa3_half_tiles": _geom(B=2, Hq=24, Hkv=8, D=128, S=4, W=32, M=64, P=1500, dtype="bf16", ncomp=96, seed=203),
     "fast_ragged": _geom(B=2, Hq=8, Hkv=4, D=32, S=2, W=9, M=16, P=901, ragged=True, seed=204),
     "fast_one_kv_head": _geom(B=3, Hq=4, Hkv=1, D=128, S=4, W=33, M=16, P=777, ncomp=96, seed=205),
     "fast_nothing_verbatim": _geom(B=1, Hq=4, Hkv=2, D=16, W=6, M=16, P=800, ncomp=16, seed=206),
