@@ -59,9 +59,9 @@ def _load():
     lib.fa_last_error_string.restype = C.c_char_p
     lib.fa_gather_cols.argtypes = [vp, C.c_int, C.c_int, C.c_int, i64, i64, vp, C.c_int, vp, i64, i64, vp]
     lib.fa_colstats.argtypes = [vp, C.c_int, C.c_int, C.c_int, i64, i64, vp, C.c_int, vp, vp, vp]
-    lib.fa_compress_scratch_bytes.argtypes = [C.c_int] * 4
+    lib.fa_compress_scratch_bytes.argtypes = [C.c_int] * 5
     lib.fa_compress_scratch_bytes.restype = sz
-    lib.fa_compress.argtypes = [vp, C.c_int, C.c_int, C.c_int, i64, i64, vp, C.c_int, C.c_int, C.c_int, i64, vp,
+    lib.fa_compress.argtypes = [vp, C.c_int, C.c_int, C.c_int, i64, i64, C.c_int, vp, C.c_int, C.c_int, C.c_int, i64, vp,
                                 C.c_int, vp, sz, vp]
     lib.fa_evict_update.argtypes = [vp, vp, i64, vp, C.c_int, vp, vp, i64, vp, C.c_int, C.c_int, C.c_int, C.c_int,
                                     i64, C.c_int, C.c_int, vp]

@@ -1,5 +1,7 @@
 // Version, per-thread error text and small shared host helpers of the C ABI.
 #include <stdarg.h>
+
+#include <mutex>
 #include <string.h>
 
 #include "common.cuh"
@@ -31,6 +33,39 @@ int sm_count() {
     cached_dev = dev;
   }
   return cached;
+}
+
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(f);
+  });
+  return fn;
+}
+
+int make_tensor_map_3d(CUtensorMap* m, const void* base, int dtype, int cols, int rows, int64_t row_stride, int B,
+                       int64_t batch_stride, int box_cols, int box_rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  FA_REQUIRE(enc != nullptr, FA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)B};
+  cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)(B > 1 ? batch_stride : row_stride * rows) * 2};
+  cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, dtype == FA_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  FA_REQUIRE(r == CUDA_SUCCESS, FA_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return FA_OK;
 }
 
 }  // namespace fa

@@ -1,6 +1,7 @@
 // Shared host/device helpers for the Fourier KV-cache kernels (sm_100a).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -108,5 +109,17 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 int sm_count();
+
+// (cols x rows x B) tiled tensor map of a 16-bit tensor, 128-byte swizzle, out-of-range elements read as 0.
+// box_cols * 2 bytes must not exceed 128.  Strides in elements.
+int make_tensor_map_3d(CUtensorMap* m, const void* base, int dtype, int cols, int rows, int64_t row_stride, int B,
+                       int64_t batch_stride, int box_cols, int box_rows);
+
+// tensor-core projection (compress_tc.cu)
+bool compress_tc_usable(const void* x, int B, int K, int64_t x_sb, int64_t x_sk, int x_cols, int N);
+size_t compress_tc_scratch_bytes(int B, int K, int N, int x_cols);
+int compress_tc_launch(const void* x, int dtype, int B, int K, int64_t x_sb, int64_t x_sk, int x_cols, const int32_t* idx,
+                       int Mc, int N, int T_c, int64_t k_start, float* coef, int accumulate, void* scratch,
+                       size_t scratch_bytes, cudaStream_t st);
 
 }  // namespace fa

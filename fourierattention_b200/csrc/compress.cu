@@ -360,25 +360,37 @@ __global__ void fourier_inverse_kernel(const float* __restrict__ c, int N, int K
 
 using namespace fa;
 
-extern "C" size_t fa_compress_scratch_bytes(int B, int K, int N, int Mc) {
-  if (B <= 0 || K <= 0 || N <= 0 || Mc <= 0) return 0;
+static size_t simt_compress_scratch_bytes(int B, int K, int N, int Mc) {
   CompressPlan p = compress_plan(B, K, N, Mc);
   if (p.nsplit <= 1) return 0;
   return (size_t)p.nsplit * B * 2 * N * Mc * sizeof(float);
 }
 
-extern "C" int fa_compress(const void* x, int dtype, int B, int K, int64_t x_sb, int64_t x_sk, const int32_t* idx,
-                           int Mc, int N, int T_c, int64_t k_start, float* coef, int accumulate, void* scratch,
-                           size_t scratch_bytes, fa_stream_t stream) {
+extern "C" size_t fa_compress_scratch_bytes(int B, int K, int N, int Mc, int x_cols) {
+  if (B <= 0 || K <= 0 || N <= 0 || Mc <= 0) return 0;
+  // the caller cannot know which path the alignment of x will select: size for the larger one
+  const size_t a = simt_compress_scratch_bytes(B, K, N, Mc);
+  const size_t b = (K >= 256 && x_cols > 0) ? compress_tc_scratch_bytes(B, K, N, x_cols) : 0;
+  return a > b ? a : b;
+}
+
+extern "C" int fa_compress(const void* x, int dtype, int B, int K, int64_t x_sb, int64_t x_sk, int x_cols,
+                           const int32_t* idx, int Mc, int N, int T_c, int64_t k_start, float* coef, int accumulate,
+                           void* scratch, size_t scratch_bytes, fa_stream_t stream) {
   FA_REQUIRE(dtype == FA_DTYPE_F16 || dtype == FA_DTYPE_BF16, FA_ERR_DTYPE, "fa_compress: bad dtype %d", dtype);
-  FA_REQUIRE(B > 0 && K > 0 && N > 0 && Mc > 0 && T_c > 0 && k_start >= 0, FA_ERR_SHAPE,
-             "fa_compress: B, K, N, Mc, T_c must be positive (got %d, %d, %d, %d, %d)", B, K, N, Mc, T_c);
+  FA_REQUIRE(B > 0 && K > 0 && N > 0 && Mc > 0 && T_c > 0 && k_start >= 0 && x_cols > 0, FA_ERR_SHAPE,
+             "fa_compress: B, K, N, Mc, T_c, x_cols must be positive (got %d, %d, %d, %d, %d, %d)", B, K, N, Mc, T_c,
+             x_cols);
+  FA_REQUIRE(idx != nullptr || Mc == x_cols, FA_ERR_SHAPE, "fa_compress: without an index list Mc must equal x_cols");
   FA_REQUIRE(x && coef, FA_ERR_NULL, "fa_compress: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (compress_tc_usable(x, B, K, x_sb, x_sk, x_cols, N))
+    return compress_tc_launch(x, dtype, B, K, x_sb, x_sk, x_cols, idx, Mc, N, T_c, k_start, coef, accumulate, scratch,
+                              scratch_bytes, st);
   CompressPlan p = compress_plan(B, K, N, Mc);
-  const size_t need = fa_compress_scratch_bytes(B, K, N, Mc);
+  const size_t need = simt_compress_scratch_bytes(B, K, N, Mc);
   FA_REQUIRE(need == 0 || (scratch && scratch_bytes >= need), FA_ERR_CAPACITY,
              "fa_compress: scratch too small (%zu < %zu bytes)", scratch_bytes, need);
-  cudaStream_t st = (cudaStream_t)stream;
   const int64_t per_b = (int64_t)2 * N * Mc;
   // a single split writes (or adds to) the coefficients directly; several splits go through
   // scratch partials and a fixed-order reduction

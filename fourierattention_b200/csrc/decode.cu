@@ -869,39 +869,6 @@ __global__ void merge_kernel(const float* __restrict__ o, const float* __restric
 // ---------------------------------------------------------------------------------------------
 constexpr int SMEM_LIMIT = 200 * 1024;
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* f = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(f);
-  });
-  return fn;
-}
-
-// (cols x rows x B) view of a verbatim store with 64 x 64 boxes
-static int make_store_map(CUtensorMap* m, const void* base, int dtype, int cols, int rows, int64_t row_stride,
-                          int B, int64_t batch_stride) {
-  EncodeTiledFn enc = encode_tiled_fn();
-  FA_REQUIRE(enc != nullptr, FA_ERR_CUDA, "fa_decode_attn: cuTensorMapEncodeTiled is not available");
-  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)B};
-  cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)(B > 1 ? batch_stride : row_stride * rows) * 2};
-  cuuint32_t box[3] = {64, 64, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(m, dtype == FA_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
-                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  FA_REQUIRE(r == CUDA_SUCCESS, FA_ERR_CUDA, "fa_decode_attn: cuTensorMapEncodeTiled failed (%d)", (int)r);
-  return FA_OK;
-}
-
 static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
   FA_REQUIRE(a.B > 0 && a.Hq > 0 && a.Hkv > 0 && a.D > 0, FA_ERR_SHAPE, "fa_decode_attn: B, Hq, Hkv, D must be positive");
   FA_REQUIRE(a.Hq % a.Hkv == 0, FA_ERR_SHAPE, "fa_decode_attn: Hq (%d) must be a multiple of Hkv (%d)", a.Hq, a.Hkv);
@@ -1165,9 +1132,9 @@ extern "C" int fa_decode_attn(const fa_decode_args_t* args, fa_stream_t stream) 
                "fa_decode_attn: window rows must be 16-byte aligned");
   FA_REQUIRE(a.q_sb % 8 == 0 || a.B == 1, FA_ERR_ALIGN, "fa_decode_attn: q batch stride must be a multiple of 8");
   if (p.fast) {
-    if (a.Mn_k > 0 && (rc = make_store_map(&p.tm_k, a.k_mn, a.dtype, a.Mn_k, a.n_mid, a.k_mn_sk, a.B, a.k_mn_sb)) != FA_OK)
+    if (a.Mn_k > 0 && (rc = make_tensor_map_3d(&p.tm_k, a.k_mn, a.dtype, a.Mn_k, a.n_mid, a.k_mn_sk, a.B, a.k_mn_sb, 64, 64)) != FA_OK)
       return rc;
-    if (a.Mn_v > 0 && (rc = make_store_map(&p.tm_v, a.v_mn, a.dtype, a.Mn_v, a.n_mid, a.v_mn_sk, a.B, a.v_mn_sb)) != FA_OK)
+    if (a.Mn_v > 0 && (rc = make_tensor_map_3d(&p.tm_v, a.v_mn, a.dtype, a.Mn_v, a.n_mid, a.v_mn_sk, a.B, a.v_mn_sb, 64, 64)) != FA_OK)
       return rc;
   }
   cudaStream_t st = (cudaStream_t)stream;

@@ -90,9 +90,9 @@ def compress(x, idx32, N, T_c, k_start=0, coef=None, accumulate=False):
     elif coef.shape != (B, 2 * N, Mc) or coef.dtype != torch.float32 or not coef.is_contiguous():
         raise ValueError("coef must be a contiguous float32 (B, 2N, Mc) tensor")
     with torch.cuda.device(x.device):
-        nbytes = lib.fa_compress_scratch_bytes(B, K, N, Mc)
+        nbytes = lib.fa_compress_scratch_bytes(B, K, N, Mc, x.shape[2])
         sc = scratch(x.device, nbytes) if nbytes else None
-        check(lib.fa_compress(_p(x), _dt(x), B, K, sb, sk, _p(idx32), Mc, N, int(T_c), int(k_start), _p(coef),
+        check(lib.fa_compress(_p(x), _dt(x), B, K, sb, sk, x.shape[2], _p(idx32), Mc, N, int(T_c), int(k_start), _p(coef),
                               int(bool(accumulate)), _p(sc), nbytes, _stream(x)), "fa_compress")
     _count(2 if nbytes else 1)
     return coef

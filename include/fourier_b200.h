@@ -69,13 +69,15 @@ int fa_colstats(const void* x, int dtype, int B, int K, int64_t x_sb, int64_t x_
 /* Forward projection of K rows onto N cosines + N sines of period T_c with phase offset k_start:
  *   coef[b,n,m]   (+)= sum_k x[b,k,idx[m]] cos(2 pi (k+k_start) n / T_c)
  *   coef[b,N+n,m] (+)= sum_k x[b,k,idx[m]] sin(2 pi (k+k_start) n / T_c)
- * idx may be null (identity, then x has Mc columns).  accumulate != 0 adds to coef.
- * scratch: fp32 device buffer of at least fa_compress_scratch_bytes(...) bytes (split-K partials,
- * reduced in a fixed order).
+ * x has x_cols valid columns per row (idx values < x_cols); idx may be null (identity, Mc == x_cols).
+ * accumulate != 0 adds to coef.  scratch: device buffer of at least fa_compress_scratch_bytes(...) bytes,
+ * 16-byte aligned (split-K partials, reduced in a fixed order).
+ * Spans of 256 rows or more whose rows are 16-byte aligned (x 16-byte aligned, strides multiples of 8) run
+ * on the tcgen05 tensor cores with TMA-staged tiles; the rest runs on CUDA cores.
  * Replaces the prefill FFT of MultiDimHiPPO2.forward (KM:857-865) and the general-K
  * mat_fourier_triton (KM:81-102, kernel KM:21-78). */
-size_t fa_compress_scratch_bytes(int B, int K, int N, int Mc);
-int fa_compress(const void* x, int dtype, int B, int K, int64_t x_sb, int64_t x_sk,
+size_t fa_compress_scratch_bytes(int B, int K, int N, int Mc, int x_cols);
+int fa_compress(const void* x, int dtype, int B, int K, int64_t x_sb, int64_t x_sk, int x_cols,
                 const int32_t* idx, int Mc, int N, int T_c, int64_t k_start, float* coef,
                 int accumulate, void* scratch, size_t scratch_bytes, fa_stream_t stream);
 

@@ -84,7 +84,7 @@ def test_validation_without_a_gpu(L):
     assert L.lib.fa_decode_attn(None, None) == -1
     assert L.lib.fa_colstats(None, 0, 1, 1, 1, 1, None, 1, None, None, None) == -1
     assert L.lib.fa_colstats(None, 5, 1, 1, 1, 1, None, 1, None, None, None) == -3
-    assert L.lib.fa_compress(None, 0, 1, 0, 1, 1, None, 1, 1, 1, 0, None, 0, None, 0, None) == -2
+    assert L.lib.fa_compress(None, 0, 1, 0, 1, 1, 1, None, 1, 1, 1, 0, None, 0, None, 0, None) == -2
     assert L.lib.fa_merge(None, None, None, 0, 1, 1, None, None) == -2
     with pytest.raises(ValueError):
         L.check(-2, "x")
@@ -93,6 +93,6 @@ def test_validation_without_a_gpu(L):
 
 
 def test_scratch_size_queries(L):
-    assert L.lib.fa_compress_scratch_bytes(1, 1, 128, 768) == 0
-    assert L.lib.fa_compress_scratch_bytes(1, 31740, 256, 768) > 0
+    assert L.lib.fa_compress_scratch_bytes(1, 1, 128, 768, 1024) == 0
+    assert L.lib.fa_compress_scratch_bytes(1, 31740, 256, 768, 1024) > 0
     assert L.lib.fa_recon_stats_scratch_bytes(8, 31740, 768) > 0

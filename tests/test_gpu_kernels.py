@@ -204,6 +204,27 @@ def test_compress_matches_oracle(dtype, B, K, F, Mc, N, T, k0):
 
 
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_compress_tensor_core_and_cuda_core_paths_agree(dtype, monkeypatch):
+    """Spans of >= 256 aligned rows run on tcgen05 (TMA-staged tiles, accumulator in tensor memory); the
+    environment variable FA_COMPRESS_SIMT forces the CUDA-core kernel.  Both must match the oracle, on a
+    shape with more than one 128-row block, more than one 256-column block and several token chunks."""
+    import fourierattention_b200.ops as ops
+    rng = np.random.default_rng(17)
+    B, K, F, N, T = 2, 4100, 320, 96, 4500
+    x = fo.rnd(rng.standard_normal((B, K, F)).astype(np.float32) * 3, dtype)
+    idx = np.sort(rng.choice(F, 200, replace=False))
+    ref = fo.fourier_project(x[:, :, idx], N, T, 3)
+    xd, idd = dev(x, dtype), dev(idx.astype(np.int32))
+    tc = host(ops.compress(xd, idd, N, T, 3))
+    monkeypatch.setenv("FA_COMPRESS_SIMT", "1")
+    simt = host(ops.compress(xd, idd, N, T, 3))
+    scale = np.abs(ref).max()
+    assert np.abs(simt - ref).max() <= 3e-6 * scale
+    assert np.abs(tc - ref).max() <= 3e-6 * scale, np.abs(tc - ref).max() / scale
+    assert not np.array_equal(tc, simt)       # two different kernels produced them
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
 def test_colstats_and_gather(dtype):
     import fourierattention_b200.ops as ops
     rng = np.random.default_rng(3)
