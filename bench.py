@@ -360,15 +360,81 @@ def ours_arm(args, w):
         dist.destroy_process_group()
 
 
+def compress_sweep(args):
+    """BASELINE config 4: the prefill projection alone, bf16, one layer, 8 KV heads x 128 dims of which 96 per
+    head are compressed (Mc = 768), K/V ~ N(0,1) x per-dim scale ~ LogUniform(0.1, 10); spans 4096..131072,
+    M in {256, 512, 1024}.  Prints one JSON line with TFLOP/s (algorithmic FLOPs 2*M*K*Mc of the compressed
+    columns only) against the measured bf16 tensor peak, and the coefficient error against a float64
+    evaluation of 24 sampled columns."""
+    import math
+    import torch
+    from fourierattention_b200 import ops, synth, compress_period
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev); gen.manual_seed(4)
+    Hkv, D, ncomp = 8, 128, 96
+    F, Mc = Hkv * D, Hkv * ncomp
+    tables = synth.make_splithead_tables(1, Hkv, D, ncomp, seed=44)["Layer_0"]
+    idx = torch.tensor(tables["kc_list"], dtype=torch.int32, device=dev)
+    peak = 1682.2
+    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(pk):
+        peak = float(json.load(open(pk))["bf16_tflops"])
+    rows = []
+    for span in (4096, 16384, 65536, 131072):
+        scale = torch.exp(torch.empty(F, device=dev).uniform_(math.log(0.1), math.log(10.0), generator=gen))
+        x = (torch.randn((1, span, F), device=dev, generator=gen) * scale).to(torch.bfloat16)
+        for M in (256, 512, 1024):
+            N = M // 2
+            T = span + 256
+            T_c = compress_period(T)
+            for _ in range(3):
+                coef = ops.compress(x, idx, N, T_c, 0)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            e0.record()
+            for _ in range(reps):
+                coef = ops.compress(x, idx, N, T_c, 0)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / reps
+            flops = 2.0 * M * span * Mc
+            # float64 check on sampled columns and frequencies
+            cols = idx[torch.arange(0, Mc, Mc // 24, device=dev)[:24]].long()
+            xs = x[0][:, cols].double()
+            n = torch.arange(0, N, max(1, N // 16), device=dev)
+            k = torch.arange(span, device=dev, dtype=torch.int64)
+            ph = (k[:, None] * n[None, :]) % T_c
+            ang = ph.double() * (2 * math.pi / T_c)
+            ref_c = torch.cos(ang).T @ xs
+            ref_s = torch.sin(ang).T @ xs
+            pos = torch.arange(0, Mc, Mc // 24, device=dev)[:24]
+            got_c = coef[0][n][:, pos].double()
+            got_s = coef[0][N + n][:, pos].double()
+            err = max(float((got_c - ref_c).abs().max()), float((got_s - ref_s).abs().max()))
+            rms = float(torch.cat([ref_c, ref_s]).pow(2).mean().sqrt())
+            rows.append({"span": span, "M": M, "ms": ms, "tflops": flops / ms / 1e9, "frac_of_peak": flops / ms / 1e9 / peak,
+                         "max_abs_err": err, "coef_rms": rms, "rel_err": err / rms, "T": T, "T_c": T_c})
+    print(json.dumps({"metric": "compression TFLOP/s (algorithmic)", "unit": "TFLOP/s", "n_gpus": 1, "dtype": "bf16",
+                      "data": "synthetic", "config": {"workload": "compress_sweep", "Mc": Mc, "source_columns": F},
+                      "roofline": {"bound": "tensor", "peak": peak, "unit": "TFLOP/s",
+                                   "note": "the kernel also multiplies the 256 uncompressed columns and uses 3 bf16 "
+                                           "terms per basis value, so its executed FLOPs are 4x the algorithmic ones"},
+                      "rows": rows}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=16)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama31_8b_32k", choices=list(WORKLOADS))
+    ap.add_argument("--workload", default="llama31_8b_32k", choices=list(WORKLOADS) + ["compress_sweep"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the host-core baseline leg")
     args = ap.parse_args()
+    if args.workload == "compress_sweep":
+        return compress_sweep(args)
     w = dict(WORKLOADS[args.workload])
     if args.impl == "reference":
         reference_arm(args, w)

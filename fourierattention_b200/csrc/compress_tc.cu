@@ -4,13 +4,14 @@
 // accumulator in tensor memory.  Per CTA: one 128-row block of the 2N basis rows, one 256-column block of
 // X, one chunk of the token axis (split-K, partials reduced afterwards in a fixed order).
 //
-// Warp roles (192 threads):
-//   warps 0-3  generate the basis tile of each stage straight into shared memory in the K-major
+// Warp roles (448 threads):
+//   warps 0-7  generate the basis tile of each stage straight into shared memory in the K-major
 //              core-matrix layout the MMA reads (exact integer phase every 8 tokens, 3 rotations between),
 //              split into 2 (fp16) or 3 (bf16) terms so that the 16-bit operand carries ~22 bits;
-//              afterwards they drain the accumulator (tcgen05.ld) to the partial buffer;
-//   warp 4     streams X tiles with TMA (64-column x 32-token boxes, 128-byte swizzle = MN-major operand);
-//   warp 5     owns tensor memory and issues the MMAs (one thread), releasing stages with tcgen05.commit.
+//   warp 8     streams X tiles with TMA (64-column x 32-token boxes, 128-byte swizzle = MN-major operand);
+//   warp 9     owns tensor memory and issues the MMAs (one thread), releasing stages with tcgen05.commit;
+//              it alternates between two accumulators, one per 256-token segment;
+//   warps 10-13 drain the finished segment's accumulator (tcgen05.ld) and add it to the CTA's partial tile.
 // Every wait is bounded; a wait that gives up sets a flag that makes the reduction write NaN.
 #include <cuda.h>
 
@@ -23,7 +24,10 @@ namespace fa {
 constexpr int TC_KT = 32;        // tokens per stage
 constexpr int TC_ST = 4;         // stages
 constexpr int TC_NC = 256;       // columns per CTA (MMA N)
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 448;
+constexpr int TC_SEG = 8;         // stages per accumulation segment (256 tokens): the tensor core adds into its
+                                 // fp32 accumulator with truncation, so chains are kept short and the segments
+                                 // are summed with round-to-nearest adds outside
 constexpr int TC_B_BYTES = 4 * TC_KT * 128;   // four 64-column boxes
 constexpr int TC_A_BYTES = 128 * TC_KT * 2;   // one term of the basis tile
 
@@ -133,12 +137,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) compress_tc_kernel(const __grid
   constexpr int NTERM = TcSplit<T>::NTERM;
   constexpr int STAGE = TC_B_BYTES + NTERM * TC_A_BYTES;
   extern __shared__ __align__(1024) unsigned char smem[];
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TC_ST * STAGE);   // full_b[ST], full_a[ST], empty[ST], acc
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TC_ST * STAGE);   // full_b, full_a, empty [ST]; acc_full/empty [2]
   uint64_t* full_b = bars;
   uint64_t* full_a = bars + TC_ST;
   uint64_t* empty = bars + 2 * TC_ST;
   uint64_t* acc_full = bars + 3 * TC_ST;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * TC_ST + 1);
+  uint64_t* acc_empty = bars + 3 * TC_ST + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * TC_ST + 4);
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -150,16 +155,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) compress_tc_kernel(const __grid
   if (tid == 0) {
     for (int s = 0; s < TC_ST; ++s) {
       tc_mbar_init(full_b + s, 1);
-      tc_mbar_init(full_a + s, 128);
+      tc_mbar_init(full_a + s, 256);
       tc_mbar_init(empty + s, 1);
     }
-    tc_mbar_init(acc_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      tc_mbar_init(acc_full + i, 1);
+      tc_mbar_init(acc_empty + i, 128);
+    }
     *dead = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)),
-                 "r"(TC_NC) : "memory");
+                 "r"(2 * TC_NC) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -167,9 +175,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) compress_tc_kernel(const __grid
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const uint32_t tmem = *tmem_slot;
 
-  if (warp < 4) {
-    // ---- basis generators ---------------------------------------------------------------------
-    const int r = tid;                      // row of the 128-row block
+  if (warp < 8) {
+    // ---- basis generators (warps 0-3: tokens 0-15 of a stage, warps 4-7: tokens 16-31) ---------------------------------------------------------------------
+    const int r = tid & 127;                // row of the 128-row block
+    const int th = tid >> 7;                // which half of the stage's tokens
     const int R = rb * 128 + r;             // row of the 2N x C result
     const bool live = R < 2 * p.N;
     const bool is_sin = R >= p.N;
@@ -183,7 +192,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) compress_tc_kernel(const __grid
       unsigned char* abase = smem + s * STAGE + TC_B_BYTES + (r >> 3) * 512 + (r & 7) * 16;
       const uint64_t pos0 = p.k_start + (uint64_t)(kbeg + it * TC_KT);
 #pragma unroll
-      for (int g8 = 0; g8 < TC_KT / 8; ++g8) {
+      for (int g8 = 2 * th; g8 < 2 * th + 2; ++g8) {
         float sv, cv;
         sincos_phase(phase_mod(pos0 + 8 * g8, n, p.T_c), inv_T, &sv, &cv);
         uint16_t tt[3][8];
@@ -210,24 +219,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) compress_tc_kernel(const __grid
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic writes -> MMA reads
       tc_mbar_arrive(full_a + s);
     }
-    // ---- epilogue: accumulator -> partial buffer -------------------------------------------------
-    tc_mbar_wait(acc_full, 0, dead, p.err);
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    float* dst = p.part + (int64_t)split * p.split_stride + (int64_t)b * p.b_stride + (int64_t)R * p.C + cb * TC_NC;
-#pragma unroll 1
-    for (int c = 0; c < TC_NC / 32; ++c) {
-      float v[32];
-      tc_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), v);
-      if (live) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = cb * TC_NC + c * 32 + i;
-          if (col < p.C) dst[c * 32 + i] = (nkt > 0) ? v[i] : 0.f;
-        }
-      }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     // ---- TMA producer ----------------------------------------------------------------------------
     if (lane == 0) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&p.tm_x) : "memory");
     for (int it = 0; it < nkt; ++it) {
@@ -239,13 +231,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) compress_tc_kernel(const __grid
         tc_tma_box(smem + s * STAGE + lane * (TC_KT * 128), &p.tm_x, cb * TC_NC + 64 * lane, kbeg + it * TC_KT, b,
                    full_b + s);
     }
-  } else {
+  } else if (warp == 9) {
     // ---- MMA issuer ------------------------------------------------------------------------------
     // instruction descriptor: fp32 accumulate, A K-major, B MN-major, N = 256, M = 128
     const uint32_t idesc = (1u << 4) | (TcSplit<T>::FMT << 7) | (TcSplit<T>::FMT << 10) | (1u << 16) |
                            ((uint32_t)(TC_NC >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     for (int it = 0; it < nkt; ++it) {
       const int s = it % TC_ST;
+      const int sg = it / TC_SEG, acc = sg & 1;
+      const bool seg_first = (it % TC_SEG) == 0, seg_last = ((it % TC_SEG) == TC_SEG - 1) || (it == nkt - 1);
+      if (seg_first && sg >= 2) tc_mbar_wait(acc_empty + acc, ((sg >> 1) - 1) & 1, dead, p.err);   // drained
       tc_mbar_wait(full_a + s, (it / TC_ST) & 1, dead, p.err);
       tc_mbar_wait(full_b + s, (it / TC_ST) & 1, dead, p.err);
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -259,19 +254,65 @@ __global__ void __launch_bounds__(TC_THREADS, 1) compress_tc_kernel(const __grid
           for (int e = 0; e < NTERM; ++e) {
             // A: core matrices of 8 rows x 8 tokens; K-adjacent ones 128 bytes apart, 8-row groups 512 bytes
             const uint64_t ad = tc_desc(asm_ + e * TC_A_BYTES + kk * 256, 128, 512, 0);
-            tc_mma(tmem, ad, bd, idesc, (it > 0 || kk > 0 || e > 0) ? 1u : 0u);
+            tc_mma(tmem + acc * TC_NC, ad, bd, idesc, (!seg_first || kk > 0 || e > 0) ? 1u : 0u);
           }
         }
-        tc_commit(empty + s);   // arrives when the MMAs above have finished reading the stage
+        tc_commit(empty + s);                      // arrives when the MMAs above have finished reading the stage
+        if (seg_last) tc_commit(acc_full + acc);   // ... and when the segment's accumulator is complete
       }
       __syncwarp();
     }
-    if (lane == 0) tc_commit(acc_full);
+  } else {
+    // ---- segment drain: accumulator -> running partial tile (round-to-nearest adds) ---------------
+    const int q = warp & 3;                    // tensor-memory lane quadrant this warp may read
+    // rows of this warp: rb*128 + q*32 + (0..31).  A 32 x 32 block leaves tensor memory one row per lane;
+    // it is turned through shared memory so that the global read-modify-write runs along the columns.
+    float* tile = reinterpret_cast<float*>(smem + TC_ST * STAGE + 256) + q * (32 * 33);
+    const int R0 = rb * 128 + q * 32;
+    float* dst0 = p.part + (int64_t)split * p.split_stride + (int64_t)b * p.b_stride + (int64_t)R0 * p.C + cb * TC_NC;
+    const int nseg = (nkt + TC_SEG - 1) / TC_SEG;
+    if (nseg == 0) {
+      for (int j = 0; j < 32; ++j)
+        for (int i = lane; i < TC_NC; i += 32)
+          if (R0 + j < 2 * p.N && cb * TC_NC + i < p.C) dst0[(int64_t)j * p.C + i] = 0.f;
+    }
+    for (int sg = 0; sg < nseg; ++sg) {
+      const int acc = sg & 1;
+      tc_mbar_wait(acc_full + acc, (sg >> 1) & 1, dead, p.err);
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll 1
+      for (int c = 0; c < TC_NC / 32; ++c) {
+        const int col = cb * TC_NC + c * 32 + lane;
+        const bool col_ok = col < p.C;
+        // the running sums of this 32 x 32 block are requested first, so their latency overlaps the
+        // tensor-memory read and the turn through shared memory
+        float old[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          old[j] = (sg > 0 && col_ok && R0 + j < 2 * p.N) ? dst0[(int64_t)j * p.C + c * 32 + lane] : 0.f;
+        float v[32];
+        tc_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * TC_NC + c * 32), v);
+        if (c == TC_NC / 32 - 1) {
+          asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+          tc_mbar_arrive(acc_empty + acc);     // the accumulator may be overwritten
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) tile[lane * 33 + i] = v[i];
+        __syncwarp();
+        if (col_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (R0 + j < 2 * p.N) dst0[(int64_t)j * p.C + c * 32 + lane] = old[j] + tile[j * 33 + lane];
+        }
+        __syncwarp();
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   }
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TC_NC) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(2 * TC_NC) : "memory");
   }
 }
 
@@ -327,7 +368,7 @@ size_t compress_tc_scratch_bytes(int B, int K, int N, int x_cols) {
 
 template <typename T>
 static int tc_launch_t(const TcParams& prm, const TcPlan& pl, int B, cudaStream_t st) {
-  constexpr int smem = TC_ST * (TC_B_BYTES + TcSplit<T>::NTERM * TC_A_BYTES) + 256;
+  constexpr int smem = TC_ST * (TC_B_BYTES + TcSplit<T>::NTERM * TC_A_BYTES) + 256 + 4 * 32 * 33 * 4;
   cudaError_t e = cudaFuncSetAttribute(compress_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(compress_tc)");
   dim3 grid(pl.n_rb * pl.n_cb, pl.nsplit, B);

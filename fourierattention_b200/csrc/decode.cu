@@ -696,13 +696,14 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) decode_main_kernel(const __gri
 
 #include "decode_fast.cuh"
 
-constexpr int FAST_THREADS = DEC_THREADS;
+constexpr int FAST_THREADS = FAST_T;
 
 template <typename T, int NT, int NH>
 __global__ void __launch_bounds__(FAST_THREADS, 1) decode_main_fast_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int b = blockIdx.y;
   if ((int)blockIdx.x < p.n_il_chunks) {
+    if (threadIdx.x >= DEC_THREADS) return;   // the sinks+window pass is written for 256 threads
     il_chunk<T>(p, b, blockIdx.x, smem_raw);
   } else {
     mid_chunk_fast<T, NT, NH>(p, b, blockIdx.x - p.n_il_chunks, smem_raw);

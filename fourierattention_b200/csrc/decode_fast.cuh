@@ -41,6 +41,10 @@ __device__ unsigned long long g_phase_clk[16];
 constexpr int FD = 16;   // interpolation nodes per super-tile
 constexpr int FH = 64;   // tokens per half tile (staging granularity)
 constexpr int FNT_MAX = 4;
+constexpr int FW = 16;            // warps of a middle-span CTA
+constexpr int FAST_T = 32 * FW;   // its threads
+constexpr int FNG = FW / 4;       // column-tile groups: warp = (16-token slice w & 3, group w >> 2)
+constexpr int FNI = (FNT_MAX + FNG - 1) / FNG;   // column tiles a warp visits
 
 __constant__ int c_nodes128[FD] = {0, 3, 7, 14, 23, 34, 45, 57, 70, 82, 93, 104, 113, 120, 124, 127};
 __constant__ int c_nodes64[FD] = {0, 1, 4, 7, 12, 17, 22, 28, 35, 41, 46, 51, 56, 59, 62, 63};
@@ -78,7 +82,7 @@ __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], const uin
 }
 
 // ---- async-copy pipeline primitives ---------------------------------------------------------------
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;\n" ::: "memory"); }
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(FAST_T) : "memory"); }
 __device__ __forceinline__ void mbar_init(void* bar, int count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
@@ -173,7 +177,7 @@ __host__ __device__ inline FastSmem fast_smem(int N, int NT, int NH, int Mn_k, i
   s.rot = take(N * 8);
   s.ph = take(N * 4);
   s.dJ = take(N * 4);
-  s.snode32 = take(2 * FD * HN * 4);   // two partial sums (halves of the 2N rows)
+  s.snode32 = take(FNG * FD * HN * 4);   // partial sums over parts of the 2N rows
   s.snode_hi = take(HN * 24 * 2);
   s.snode_lo = take(HN * 24 * 2);
   s.pt_b = take(HN * 24 * 2);
@@ -211,9 +215,9 @@ template <typename T, int NT, int NH>
 __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned char* smem) {
   constexpr int HN = 8 * NT;
   constexpr int J = FH * NH;
-  constexpr int KH = 16;   // k16 steps of the node contraction per warp: one column tile, half of 2N <= 512
-  constexpr int MT = 4;    // 16-row tiles of g per warp
-  constexpr int MTW = 2;   // 16-column tiles of verbatim V per warp (Mn_v <= 256)
+  constexpr int KH = 32 / FNG;   // k16 steps of the node contraction per warp: one column tile, 1/FNG of 2N <= 512
+  constexpr int MT = 32 / FW;    // 16-row tiles of g per warp
+  constexpr int MTW = 16 / FW;   // 16-column tiles of verbatim V per warp (Mn_v <= 256)
   const fa_decode_args_t& a = p.a;
   const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
   const int gq = lane >> 2, tq = lane & 3;
@@ -259,7 +263,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
   const int n_loads = nst * NH * 2;            // K and V half tiles, in consumption order
   // (node, frequency-pair) walk of this thread through the node-basis table
   const int halfN = N / 2;
-  const int fk0 = tid / halfN, fp0 = tid % halfN, fdk = DEC_THREADS / halfN, fdp = DEC_THREADS % halfN;
+  const int fk0 = tid / halfN, fp0 = tid % halfN, fdk = FAST_T / halfN, fdp = FAST_T % halfN;
 
 #ifdef FA_PHASE_TIMING
   long long tick__ = clock64();
@@ -271,7 +275,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars);   // full[0..2]
   volatile int* dead = reinterpret_cast<volatile int*>(bars + 6);
   // zero everything that is read but never (or only partly) written later
-  for (int e = tid; e < (L.qn - L.fnt_hi) / 16; e += DEC_THREADS)
+  for (int e = tid; e < (L.qn - L.fnt_hi) / 16; e += FAST_T)
     reinterpret_cast<uint4*>(smem + L.fnt_hi)[e] = make_uint4(0u, 0u, 0u, 0u);
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) mbar_init(bars + i, 1);   // completed by expect_tx + the copied bytes
@@ -284,7 +288,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
   int issued = 0, issue_slot = 0;   // next half tile to request and its ring slot (warp 7)
   int consumed = 0;                 // half tiles this warp has finished reading
   auto issue_upto = [&](int limit) {
-    if (wp != 7) return;
+    if (wp != FW - 1) return;
     if (limit > n_loads) limit = n_loads;
     while (issued < limit) {
       const int i = issued;
@@ -301,13 +305,13 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
       ++issued;
     }
   };
-  if (tid == 7 * 32) {
+  if (tid == (FW - 1) * 32) {
     if (nbK) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&p.tm_k) : "memory");
     if (nbV) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&p.tm_v) : "memory");
   }
   issue_upto(3);
 
-  for (int e = tid; e < FD * N; e += DEC_THREADS) {
+  for (int e = tid; e < FD * N; e += FAST_T) {
     const int k = e / N, n = e - k * N;
     float s, c;
     sincos_phase(phase_mod((uint64_t)nodes[k], (uint32_t)n, T_), inv_T, &s, &c);
@@ -316,7 +320,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
   }
   {
     const float* tab = (NH == 2) ? g_interp128 : g_interp64;
-    for (int e = tid; e < J * FD; e += DEC_THREADS) {
+    for (int e = tid; e < J * FD; e += FAST_T) {
       const int j = e / FD, k = e - j * FD;
       __half hi, lo;
       split_h(tab[e], hi, lo);
@@ -324,7 +328,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
       interp_lo[j * 24 + k] = lo;
     }
   }
-  for (int n = tid; n < N; n += DEC_THREADS) {
+  for (int n = tid; n < N; n += FAST_T) {
     dJ[n] = phase_mod((uint64_t)J, (uint32_t)n, T_);
     ph[n] = phase_mod((uint64_t)a.mid_l0 + (uint64_t)l0, (uint32_t)n, T_);
   }
@@ -332,7 +336,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
     // block-diagonal verbatim-K query matrix, raw model-dtype values (the scale is applied to the fp32 sum)
     const T* q = reinterpret_cast<const T*>(a.q) + (int64_t)b * a.q_sb;
     const int w16 = qpitch - 8;
-    for (int e = tid; e < HN * w16; e += DEC_THREADS) {
+    for (int e = tid; e < HN * w16; e += FAST_T) {
       const int h = e / w16, col = e - h * w16;
       T v = from_f32<T>(0.f);
       if (h < Hq && col < Mn_k) {
@@ -342,7 +346,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
       qn[h * qpitch + col] = v;
     }
   }
-  for (int h = tid; h < HN; h += DEC_THREADS) {
+  for (int h = tid; h < HN; h += FAST_T) {
     alpha[h] = 1.f;
     alpha_prod[h] = 1.f;
     m_run[h] = NEG_BIG;
@@ -362,23 +366,23 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
     kcol[2 * tid] = c0;
     kcol[2 * tid + 1] = c1;
   }
-  for (int c = tid; c < Mn_v; c += DEC_THREADS) {
+  for (int c = tid; c < Mn_v; c += FAST_T) {
     int g = 0;
     while (g + 1 < a.Hkv && c >= a.vn_h[g + 1]) ++g;
     vhead[c] = (int16_t)g;
   }
   consumer_sync();
-  for (int mt = tid; mt * 16 < Mn_v; mt += DEC_THREADS) {
+  for (int mt = tid; mt * 16 < Mn_v; mt += FAST_T) {
     const int g_first = vhead[16 * mt], g_last = vhead[min(Mn_v, 16 * mt + 16) - 1];
     vnt[2 * mt] = (R * g_first) / 8;
     vnt[2 * mt + 1] = (R * (g_last + 1) - 1) / 8;
   }
 
   // w as persistent B fragments (hi / lo halves): k = frequency row, n = head.  Warp w holds column tile
-  // w & 3 for the lower (w < 4) or upper half of the 2N rows.
+  // w & 3 for part w >> 2 of the 2N rows.
   const int nt1 = wp & 3, khalf = wp >> 2;
   const int ktot = kpad / 16;            // k16 steps of the node contraction == 16-row tiles of g
-  const int kh_steps = (ktot + 1) / 2;   // steps per half
+  const int kh_steps = (ktot + FNG - 1) / FNG;   // steps per part
   uint32_t bhi[KH][2], blo[KH][2];
   {
     const float* wb = p.w + (int64_t)b * Hq * 2 * N;
@@ -418,7 +422,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) Oacc[i][nt][e] = 0.f;
-  const int mt4 = wp & 3, ntp = wp >> 2;
+  const int mt4 = wp & 3, ntp = wp >> 2;   // 16-token slice of a half tile, column-tile group
   consumer_sync();
 
   FA_TICK(0);
@@ -428,7 +432,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
   for (int st = 0; st < nst; ++st) {
     const int st_tok0 = l0 + st * J;
     // ---- A: node basis of this super-tile ----------------------------------------------------
-    for (int n = tid; n < N; n += DEC_THREADS) {
+    for (int n = tid; n < N; n += FAST_T) {
       float s, c;
       const uint32_t v = ph[n];
       sincos_phase(v, inv_T, &s, &c);
@@ -490,10 +494,13 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
       red[(gq + 8) * HN + col + 1] = (acc[0][3] + acc[1][3]) + (acc[2][3] + acc[3][3]);
     }
     consumer_sync();
-    for (int e = tid; e < FD * HN; e += DEC_THREADS) {
+    for (int e = tid; e < FD * HN; e += FAST_T) {
       const int k = e / HN, h = e - k * HN;
       __half hi, lo;
-      split_h(snode32[e] + snode32[FD * HN + e], hi, lo);
+      float sv = 0.f;
+#pragma unroll
+      for (int part = 0; part < FNG; ++part) sv += snode32[part * FD * HN + e];
+      split_h(sv, hi, lo);
       snode_hi[h * 24 + k] = hi;
       snode_lo[h * 24 + k] = lo;
     }
@@ -505,9 +512,9 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
     for (int half = 0; half < NH; ++half) {
       const int tok0 = st_tok0 + half * FH;    // first token of this half
       // ---- C: interpolate the node scores to this warp's 16 tokens ---------------------------
-      float sc[2][4];
+      float sc[FNI][4];
 #pragma unroll
-      for (int i = 0; i < 2; ++i)
+      for (int i = 0; i < FNI; ++i)
 #pragma unroll
         for (int e = 0; e < 4; ++e) sc[i][e] = 0.f;
       {
@@ -516,8 +523,8 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
         ldsm_x4(ah, interp_hi + off);
         ldsm_x4(al, interp_lo + off);
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int nt = ntp + 2 * i;
+        for (int i = 0; i < FNI; ++i) {
+          const int nt = ntp + FNG * i;
           if (nt < NT) {
             uint32_t bh[2], bl[2];
             const int boff = (8 * nt + lds_b_row(lane)) * 24 + lds_b_col(lane);
@@ -536,8 +543,8 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
       {
         const unsigned char* ks_ = reinterpret_cast<const unsigned char*>(slots) + use_slot * L.slot_bytes;
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int nt = ntp + 2 * i;
+        for (int i = 0; i < FNI; ++i) {
+          const int nt = ntp + FNG * i;
           if (nt < NT) {
             float vb[4] = {0.f, 0.f, 0.f, 0.f};
             const int c_end = kcol[2 * nt + 1];
@@ -565,8 +572,8 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
       // ---- E: online softmax over the 64 tokens of this half -----------------------------------
       const bool ok0 = (tok0 + 16 * mt4 + gq) < l1, ok1 = (tok0 + 16 * mt4 + gq + 8) < l1;
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int nt = ntp + 2 * i;
+      for (int i = 0; i < FNI; ++i) {
+        const int nt = ntp + FNG * i;
         if (nt < NT) {
           float v0 = fmaxf(ok0 ? sc[i][0] : NEG_BIG, ok1 ? sc[i][2] : NEG_BIG);
           float v1 = fmaxf(ok0 ? sc[i][1] : NEG_BIG, ok1 ? sc[i][3] : NEG_BIG);
@@ -584,8 +591,8 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
       consumer_sync();
       issue_upto(consumed + 3);   // every warp is past its reads of the half tiles consumed so far
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int nt = ntp + 2 * i;
+      for (int i = 0; i < FNI; ++i) {
+        const int nt = ntp + FNG * i;
         if (nt < NT) {
           const int col = 8 * nt + 2 * tq;
           const float mo0 = m_run[mbuf * HN + col], mo1 = m_run[mbuf * HN + col + 1];
@@ -669,7 +676,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
         const unsigned char* vs_ = reinterpret_cast<const unsigned char*>(slots) + use_slot * L.slot_bytes;
 #pragma unroll
         for (int i = 0; i < MTW; ++i) {
-          const int mt = wp + 8 * i;
+          const int mt = wp + FW * i;
           if (16 * mt < Mn_v) {
             const int nlo = vnt[2 * mt], nhi = vnt[2 * mt + 1];
 #pragma unroll
@@ -733,7 +740,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
       }
 #pragma unroll
       for (int i = 0; i < MT; ++i) {
-        const int mt = wp + 8 * i;
+        const int mt = wp + FW * i;
         if (mt < ktot) {
           uint32_t ah[4], al[4];
           const int off = lds_at_row(lane) * fpitch + 16 * mt + lds_at_col(lane);
@@ -751,23 +758,23 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
       }
     }
     consumer_sync();
-    for (int h = tid; h < HN; h += DEC_THREADS) alpha_prod[h] = 1.f;
+    for (int h = tid; h < HN; h += FAST_T) alpha_prod[h] = 1.f;
     FA_TICK(10);
   }
   consumer_sync();
 
   // ---- chunk partials ---------------------------------------------------------------------------
   const int64_t slot = (int64_t)b * p.NCH + p.n_il_chunks + chunk;
-  for (int h = tid; h < Hq; h += DEC_THREADS) {
+  for (int h = tid; h < Hq; h += FAST_T) {
     p.m_part[slot * Hq + h] = m_run[mbuf * HN + h];
     p.l_part[slot * Hq + h] = (ssum[h] + ssum[HN + h]) + (ssum[2 * HN + h] + ssum[3 * HN + h]);
   }
   float* ob = p.o_part + slot * Hq * D;
-  for (int e = tid; e < Hq * D; e += DEC_THREADS) ob[e] = 0.f;
+  for (int e = tid; e < Hq * D; e += FAST_T) ob[e] = 0.f;
   consumer_sync();
 #pragma unroll
   for (int i = 0; i < MTW; ++i) {
-    const int mt = wp + 8 * i;
+    const int mt = wp + FW * i;
     if (16 * mt < Mn_v) {
       const int nlo = vnt[2 * mt], nhi = vnt[2 * mt + 1];
 #pragma unroll
@@ -789,7 +796,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
   float* gb = p.g_part + (((int64_t)b * p.n_mid_chunks + chunk) * Hq) * 2 * N;
 #pragma unroll
   for (int i = 0; i < MT; ++i) {
-    const int mt = wp + 8 * i;
+    const int mt = wp + FW * i;
     if (mt < ktot) {
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
