@@ -20,8 +20,8 @@
 // reach the scores (three MMAs per product); probabilities are rounded once to 16 bits, as any
 // flash-attention kernel does.  The verbatim dims are plain GEMMs of the cached rows against a
 // block-diagonal query matrix (QK) and of the probabilities against the cached rows (PV), in the
-// model dtype.  K/V rows stream through a 3-slot ring of 64-token half tiles filled by 128-bit
-// cp.async.
+// model dtype.  K/V rows stream through a 3-slot ring of 64-token half tiles that the last warp
+// fills with TMA tensor-map boxes (64 columns x 64 tokens, 128-byte swizzle) completing on mbarriers.
 #pragma once
 
 #ifdef FA_PHASE_TIMING
