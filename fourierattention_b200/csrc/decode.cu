@@ -43,13 +43,12 @@ struct DecodeParams {
   // plan
   int J, kvh, HG, HGp, n_groups, TR, Hqp;
   int il_chunk_rows, n_il_chunks, mid_chunk, n_mid_chunks, NCH;
-  int n_rb, rb_rows;
   int pitchK, pitchV, qpitch;
-  int smem_main, smem_prepare, smem_contract;
+  int smem_main, smem_prepare;
   int force_exact;     // debugging / testing aid: never pick the tensor-core pass
   int fast, fNT, fNH;  // tensor-core middle-span pass: column tiles of 8 heads, halves per super-tile
   // scratch
-  float *w, *cst, *m_part, *l_part, *o_part, *g_part, *cv_part;
+  float *w, *cst, *m_part, *l_part, *o_part, *g_part;
   int* err;  // set by a kernel whose bounded wait gave up; the output kernel then poisons the result
   int64_t scratch_floats;
 };
@@ -98,65 +97,70 @@ __host__ __device__ inline int il_smem_bytes(int TR, int F, int Hq, int Hqp, int
 
 // ---------------------------------------------------------------------------------------------
 // prepare: w[b,h,n] = (c2/N) sum_c C_k[b,n,c] scale_k[b,c] q[b,h,dim(c)],  cst[b,h] likewise
+// grid (blocks of 256 coefficient rows, KV head, sequence); a thread owns one row of one KV head and
+// walks the head's contiguous column segment with 128-bit loads, every load independent of the others
 // ---------------------------------------------------------------------------------------------
-constexpr int PR_ROWS = 16;
-
 template <typename T>
 __global__ void __launch_bounds__(DEC_THREADS) decode_prepare_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const fa_decode_args_t& a = p.a;
-  const int b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int R = p.R, D = a.D, Mc = a.Mc_k, N = a.N, Hkv = a.Hkv;
-  float* qs = reinterpret_cast<float*>(smem_raw);                   // [R][Mc]
-  int* kch = reinterpret_cast<int*>(qs + (size_t)R * Mc);           // [Hkv+1]
+  const int g = blockIdx.y, b = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int R = p.R, D = a.D, Mc = a.Mc_k, N = a.N;
+  const int c0 = a.kc_h[g], c1 = a.kc_h[g + 1];
+  const bool vec = (Mc & 3) == 0;                            // every row starts on a 16-byte boundary
+  const int ca = vec ? (c0 & ~3) : c0;                       // first column read
+  const int len = vec ? ((c1 - ca + 3) & ~3) : (c1 - ca);    // columns read; the pads get weight zero
+  float* qs = reinterpret_cast<float*>(smem_raw);            // [R][len] query x scale
   const T* q = reinterpret_cast<const T*>(a.q) + (int64_t)b * a.q_sb;
-  for (int i = tid; i <= Hkv; i += DEC_THREADS) kch[i] = a.kc_h[i];
-  __syncthreads();
-  for (int c = tid; c < Mc; c += DEC_THREADS) {
-    int g = 0;
-    while (g + 1 < Hkv && c >= kch[g + 1]) ++g;
-    const int d = a.kc_list[c] - g * D;
-    const float sc = a.scale_k[(int64_t)b * Mc + c];
-    for (int r = 0; r < R; ++r) qs[r * Mc + c] = to_f32(q[(g * R + r) * D + d]) * sc;
+  for (int e = tid; e < R * len; e += DEC_THREADS) {
+    const int r = e / len, c = ca + e - r * len;
+    float v = 0.f;
+    if (c >= c0 && c < c1) v = to_f32(q[(g * R + r) * D + a.kc_list[c] - g * D]) * a.scale_k[(int64_t)b * Mc + c];
+    qs[e] = v;
   }
   __syncthreads();
-  const float* Ck = a.k_coef + (int64_t)b * 2 * N * Mc;
-  const float wscale = p.c2 / (float)N;
-  const int row_end = min(2 * N, (int)(blockIdx.x + 1) * PR_ROWS);
-  for (int row = blockIdx.x * PR_ROWS + warp; row < row_end; row += DEC_THREADS / 32) {
-    const float* cr = Ck + (int64_t)row * Mc;
-    for (int g = 0; g < Hkv; ++g) {
-      float acc[R_MAX];
+  const int row = blockIdx.x * DEC_THREADS + tid;
+  if (row < 2 * N) {
+    float acc[R_MAX];
 #pragma unroll
-      for (int r = 0; r < R_MAX; ++r) acc[r] = 0.f;
-      for (int c = kch[g] + lane; c < kch[g + 1]; c += 32) {
-        const float cv = cr[c];
+    for (int r = 0; r < R_MAX; ++r) acc[r] = 0.f;
+    const float* cr = a.k_coef + ((int64_t)b * 2 * N + row) * Mc + ca;
+    if (vec) {
+#pragma unroll 4
+      for (int i = 0; i < len; i += 4) {
+        const float4 cv = __ldg(reinterpret_cast<const float4*>(cr + i));
 #pragma unroll
-        for (int r = 0; r < R_MAX; ++r)
-          if (r < R) acc[r] = fmaf(cv, qs[r * Mc + c], acc[r]);
-      }
-#pragma unroll
-      for (int r = 0; r < R_MAX; ++r) {
-        if (r < R) {
-          const float v = warp_sum(acc[r]);
-          if (lane == 0) p.w[((int64_t)b * a.Hq + g * R + r) * 2 * N + row] = v * wscale;
+        for (int r = 0; r < R_MAX; ++r) {
+          if (r < R) {
+            const float4 qv = *reinterpret_cast<const float4*>(qs + r * len + i);
+            acc[r] = fmaf(cv.x, qv.x, fmaf(cv.y, qv.y, fmaf(cv.z, qv.z, fmaf(cv.w, qv.w, acc[r]))));
+          }
         }
       }
-    }
-  }
-  if (blockIdx.x == 0 && b == 0 && tid == 0) *p.err = 0;
-  if (blockIdx.x == 0) {
-    for (int h = warp; h < a.Hq; h += DEC_THREADS / 32) {
-      const int g = h / R;
-      float acc = 0.f;
-      for (int c = kch[g] + lane; c < kch[g + 1]; c += 32) {
-        const int d = a.kc_list[c] - g * D;
-        const int64_t o = (int64_t)b * Mc + c;
-        acc = fmaf(to_f32(q[h * D + d]), a.avg_k_u[o] - a.avg_k_d[o] * a.scale_k[o], acc);
+    } else {
+#pragma unroll 4
+      for (int i = 0; i < len; ++i) {
+        const float cv = __ldg(cr + i);
+#pragma unroll
+        for (int r = 0; r < R_MAX; ++r)
+          if (r < R) acc[r] = fmaf(cv, qs[r * len + i], acc[r]);
       }
-      acc = warp_sum(acc);
-      if (lane == 0) p.cst[(int64_t)b * a.Hq + h] = acc * p.c2;
     }
+    const float wscale = p.c2 / (float)N;
+#pragma unroll
+    for (int r = 0; r < R_MAX; ++r)
+      if (r < R) p.w[((int64_t)b * a.Hq + g * R + r) * 2 * N + row] = acc[r] * wscale;
+  }
+  if (blockIdx.x == 0 && g == 0 && b == 0 && tid == 0) *p.err = 0;
+  if (blockIdx.x == 0 && warp < R) {
+    const int h = g * R + warp;
+    float acc = 0.f;
+    for (int c = c0 + lane; c < c1; c += 32) {
+      const int64_t o = (int64_t)b * Mc + c;
+      acc = fmaf(to_f32(q[h * D + a.kc_list[c] - g * D]), a.avg_k_u[o] - a.avg_k_d[o] * a.scale_k[o], acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) p.cst[(int64_t)b * a.Hq + h] = acc * p.c2;
   }
 }
 
@@ -702,94 +706,45 @@ template <typename T, int NT, int NH>
 __global__ void __launch_bounds__(FAST_THREADS, 1) decode_main_fast_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int b = blockIdx.y;
+#ifdef FA_PHASE_TIMING
+  const long long cta_t0 = clock64();
+#endif
   if ((int)blockIdx.x < p.n_il_chunks) {
     if (threadIdx.x >= DEC_THREADS) return;   // the sinks+window pass is written for 256 threads
     il_chunk<T>(p, b, blockIdx.x, smem_raw);
   } else {
     mid_chunk_fast<T, NT, NH>(p, b, blockIdx.x - p.n_il_chunks, smem_raw);
   }
-}
-
-// merge weights of every chunk slot for head h:  a_i = 2^(m_i - m*)  (0 for an empty slot)
-__device__ __forceinline__ float slot_max(const DecodeParams& p, int b, int h) {
-  float ms = NEG_BIG;
-  for (int i = 0; i < p.NCH; ++i) {
-    const int64_t o = ((int64_t)b * p.NCH + i) * p.a.Hq + h;
-    if (p.l_part[o] > 0.f) ms = fmaxf(ms, p.m_part[o]);
-  }
-  return ms;
+#ifdef FA_PHASE_TIMING
+  if (threadIdx.x == 0)
+    atomicAdd(&g_phase_clk[(int)blockIdx.x < p.n_il_chunks ? 12 : 13], (unsigned long long)(clock64() - cta_t0));
+#endif
 }
 
 // ---------------------------------------------------------------------------------------------
-// contract: G*[h,n] = sum_chunks a_i g_i[h,n];  cv[rb][r][c] = sum_{n in block} G*[gR+r,n] C_v[n,c]
+// finish, one CTA per (query head, sequence): merge weights a_i = 2^(m_i - m*) of the chunk slots,
+// G*[n] = sum_chunks a_i g_i[h,n], the compressed-V dims  (1/N) sum_n G*[n] C_v[n,c]  of the head's
+// column segment, the merged verbatim numerators, normalisation
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(DEC_THREADS) decode_contract_kernel(const __grid_constant__ DecodeParams p) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const fa_decode_args_t& a = p.a;
-  const int rb = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
-  const int N = a.N, Hq = a.Hq, R = p.R, Mc = a.Mc_v, NM = p.n_mid_chunks, rows = p.rb_rows;
-  float* am = reinterpret_cast<float*>(smem_raw);       // [NM][Hq]
-  float* Gm = am + NM * Hq;                             // [2][Hq][rows]
-  int* vch = reinterpret_cast<int*>(Gm + 2 * Hq * rows);  // [Hkv+1]
-  const int r0 = rb * rows, r1 = min(N, r0 + rows);
-  for (int i = tid; i <= a.Hkv; i += DEC_THREADS) vch[i] = a.vc_h[i];
-  for (int h = tid; h < Hq; h += DEC_THREADS) {
-    const float ms = slot_max(p, b, h);
-    for (int i = 0; i < NM; ++i) {
-      const int64_t o = ((int64_t)b * p.NCH + p.n_il_chunks + i) * Hq + h;
-      am[i * Hq + h] = (p.l_part[o] > 0.f) ? exp2f(p.m_part[o] - ms) : 0.f;
-    }
-  }
-  __syncthreads();
-  for (int e = tid; e < 2 * Hq * rows; e += DEC_THREADS) {
-    const int rr = e % rows, h = (e / rows) % Hq, half = e / (rows * Hq);
-    float acc = 0.f;
-    if (r0 + rr < r1) {
-      const int n = half * N + r0 + rr;
-      for (int i = 0; i < NM; ++i)
-        acc = fmaf(am[i * Hq + h], p.g_part[(((int64_t)b * NM + i) * Hq + h) * 2 * N + n], acc);
-    }
-    Gm[e] = acc;
-  }
-  __syncthreads();
-  const float* Cv = a.v_coef + (int64_t)b * 2 * N * Mc;
-  for (int c = tid; c < Mc; c += DEC_THREADS) {
-    int g = 0;
-    while (g + 1 < a.Hkv && c >= vch[g + 1]) ++g;
-    float acc[R_MAX];
-#pragma unroll
-    for (int r = 0; r < R_MAX; ++r) acc[r] = 0.f;
-    for (int rr = 0; rr < r1 - r0; ++rr) {
-      const float cc = Cv[(int64_t)(r0 + rr) * Mc + c];
-      const float cs = Cv[(int64_t)(N + r0 + rr) * Mc + c];
-#pragma unroll
-      for (int r = 0; r < R_MAX; ++r) {
-        if (r < R) {
-          const int h = g * R + r;
-          acc[r] = fmaf(Gm[h * rows + rr], cc, fmaf(Gm[(Hq + h) * rows + rr], cs, acc[r]));
-        }
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < R_MAX; ++r)
-      if (r < R) p.cv_part[(((int64_t)b * p.n_rb + rb) * R + r) * Mc + c] = acc[r];
-  }
+constexpr int FIN_THREADS = 512;
+
+__host__ __device__ inline int finish_smem_bytes(int NCH, int N, int D) {
+  return (rup(NCH, 4) + 2 * N + rup(D, 4) + 4 * FIN_THREADS) * 4;
 }
 
-// ---------------------------------------------------------------------------------------------
-// output: merge numerators / denominators, add the compressed-V dims, normalise
-// ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) decode_output_kernel(const __grid_constant__ DecodeParams p) {
+__global__ void __launch_bounds__(FIN_THREADS) decode_finish_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const fa_decode_args_t& a = p.a;
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
-  const int D = a.D, Hq = a.Hq, R = p.R, N = a.N, Mc = a.Mc_v, NCH = p.NCH;
-  float* aw = reinterpret_cast<float*>(smem_raw);  // [NCH]
-  float* O = aw + NCH;                             // [D]
+  const int D = a.D, Hq = a.Hq, R = p.R, N = a.N, Mc = a.Mc_v, NCH = p.NCH, NM = p.n_mid_chunks;
+  const bool mid = a.n_mid > 0;
+  float* aw = reinterpret_cast<float*>(smem_raw);   // [NCH]
+  float* Gs = aw + rup(NCH, 4);                     // [2N]
+  float* O = Gs + 2 * N;                            // [D]
+  float* red = O + rup(D, 4);                       // [FIN_THREADS][4]
   __shared__ float s_L, s_P, s_ms;
-  const int g = h / R, r = h - g * R;
+  const int g = h / R;
   if (tid < 32) {
-    // one warp computes the weights
     float ms = NEG_BIG;
     for (int i = tid; i < NCH; i += 32) {
       const int64_t o = ((int64_t)b * NCH + i) * Hq + h;
@@ -814,29 +769,67 @@ __global__ void __launch_bounds__(128) decode_output_kernel(const __grid_constan
     }
   }
   __syncthreads();
-  for (int d = tid; d < D; d += blockDim.x) {
+  if (mid) {
+    for (int n = tid; n < 2 * N; n += FIN_THREADS) {
+      const float* gp = p.g_part + ((int64_t)b * NM * Hq + h) * 2 * N + n;
+      float acc = 0.f;
+#pragma unroll 4
+      for (int i = 0; i < NM; ++i) acc = fmaf(aw[p.n_il_chunks + i], gp[(int64_t)i * Hq * 2 * N], acc);
+      Gs[n] = acc;
+    }
+  }
+  for (int d = tid; d < D; d += FIN_THREADS) {
+    const float* op = p.o_part + ((int64_t)b * NCH * Hq + h) * D + d;
     float acc = 0.f;
-    for (int i = 0; i < NCH; ++i) acc = fmaf(aw[i], p.o_part[(((int64_t)b * NCH + i) * Hq + h) * D + d], acc);
+#pragma unroll 4
+    for (int i = 0; i < NCH; ++i) acc = fmaf(aw[i], op[(int64_t)i * Hq * D], acc);
     O[d] = acc;
   }
   __syncthreads();
   const float P = s_P, L = s_L;
-  if (a.n_mid > 0) {
-    const int c0 = a.vc_h[g], c1 = a.vc_h[g + 1];
-    for (int c = c0 + tid; c < c1; c += blockDim.x) {
+  const int c0 = mid ? a.vc_h[g] : 0, c1 = mid ? a.vc_h[g + 1] : 0;
+  const bool vec = (Mc & 3) == 0;   // coefficient rows start on 16-byte boundaries
+  const int W = vec ? 4 : 1;
+  const int ca = vec ? (c0 & ~3) : c0;
+  const int nck = (c1 - ca + W - 1) / W;   // column groups of the segment
+  if (nck > 0) {
+    // thread = (column group, slice of the 2N rows)
+    const int nsl = FIN_THREADS / nck;
+    const int ck = tid % nck, sl = tid / nck;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (sl < nsl) {
+      const float* cp = a.v_coef + (int64_t)b * 2 * N * Mc + ca + W * ck;
+      if (vec) {
+#pragma unroll 8
+        for (int n = sl; n < 2 * N; n += nsl) {
+          const float4 cv = __ldg(reinterpret_cast<const float4*>(cp + (int64_t)n * Mc));
+          const float gv = Gs[n];
+          acc.x = fmaf(gv, cv.x, acc.x);
+          acc.y = fmaf(gv, cv.y, acc.y);
+          acc.z = fmaf(gv, cv.z, acc.z);
+          acc.w = fmaf(gv, cv.w, acc.w);
+        }
+      } else {
+#pragma unroll 8
+        for (int n = sl; n < 2 * N; n += nsl) acc.x = fmaf(Gs[n], __ldg(cp + (int64_t)n * Mc), acc.x);
+      }
+    }
+    *reinterpret_cast<float4*>(red + 4 * tid) = acc;
+    __syncthreads();
+    for (int c = c0 + tid; c < c1; c += FIN_THREADS) {
+      const int ck2 = (c - ca) / W, e = (c - ca) - W * ck2;
       float s = 0.f;
-      for (int rb = 0; rb < p.n_rb; ++rb) s += p.cv_part[(((int64_t)b * p.n_rb + rb) * R + r) * Mc + c];
+      for (int s2 = 0; s2 < nsl; ++s2) s += red[4 * (s2 * nck + ck2) + e];
       const int64_t o = (int64_t)b * Mc + c;
       const float oc = a.scale_v[o] * (s / (float)N - a.avg_v_d[o] * P) + a.avg_v_u[o] * P;
-      const int d = a.vc_list[c] - g * D;
-      O[d] += oc;  // each compressed dim belongs to exactly one column
+      O[a.vc_list[c] - g * D] += oc;   // each compressed dim belongs to exactly one column
     }
   }
   __syncthreads();
   // a kernel of this call gave up a bounded wait: make the failure visible instead of returning numbers
-  const bool poisoned = (a.n_mid > 0) && (*p.err != 0);
+  const bool poisoned = mid && (*p.err != 0);
   const float inv = poisoned ? __int_as_float(0x7fc00000) : 1.0f / L;
-  for (int d = tid; d < D; d += blockDim.x) a.out[((int64_t)b * Hq + h) * D + d] = O[d] * inv;
+  for (int d = tid; d < D; d += FIN_THREADS) a.out[((int64_t)b * Hq + h) * D + d] = O[d] * inv;
   if (tid == 0) {
     if (a.m_out) a.m_out[(int64_t)b * Hq + h] = s_ms;
     if (a.l_out) a.l_out[(int64_t)b * Hq + h] = L;
@@ -898,7 +891,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
 
   int mid_smem_bytes = 0;
   p.J = 8; p.kvh = 1; p.HG = p.R; p.HGp = 8; p.n_groups = 1; p.pitchK = p.pitchV = 16; p.qpitch = 4;
-  p.n_mid_chunks = 0; p.mid_chunk = 8; p.n_rb = 0; p.rb_rows = 1;
+  p.n_mid_chunks = 0; p.mid_chunk = 8;
   if (a.n_mid > 0) {
     FA_REQUIRE(a.N > 0 && a.T > 0, FA_ERR_SHAPE, "fa_decode_attn: N and T must be positive");
     FA_REQUIRE(a.N <= 1024, FA_ERR_CAPACITY, "fa_decode_attn: N (%d) exceeds 1024", a.N);
@@ -960,20 +953,12 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
     if (target > max_chunks) target = max_chunks;
     p.mid_chunk = rup(ceil_div(a.n_mid, target), J);
     p.n_mid_chunks = ceil_div(a.n_mid, p.mid_chunk);
-    int nrb = ceil_div(2 * sms, a.B);
-    if (nrb > a.N) nrb = a.N;
-    if (nrb < 1) nrb = 1;
-    p.rb_rows = ceil_div(a.N, nrb);
-    p.n_rb = ceil_div(a.N, p.rb_rows);
   }
   p.NCH = p.n_il_chunks + p.n_mid_chunks;
   p.smem_main = il_smem > mid_smem_bytes ? il_smem : mid_smem_bytes;
   if (p.n_il == 0) p.smem_main = mid_smem_bytes;
   FA_REQUIRE(p.smem_main <= 227 * 1024, FA_ERR_CAPACITY, "fa_decode_attn: shared memory need %d exceeds 227 KB", p.smem_main);
-  p.smem_prepare = (p.R * a.Mc_k) * 4 + (a.Hkv + 1) * 4;
-  p.smem_contract = (p.n_mid_chunks * a.Hq + 2 * a.Hq * p.rb_rows) * 4 + (a.Hkv + 1) * 4;
-  FA_REQUIRE(p.smem_prepare <= SMEM_LIMIT && p.smem_contract <= SMEM_LIMIT, FA_ERR_CAPACITY,
-             "fa_decode_attn: helper kernels exceed shared memory");
+  p.smem_prepare = p.R * (a.D + 8) * 4;   // one KV head's column segment (at most D wide) plus alignment pads
   // scratch layout (floats, each block 16-byte aligned)
   int64_t o = 0;
   auto take = [&](int64_t n) {
@@ -984,12 +969,10 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
   const int64_t B = a.B, Hq = a.Hq;
   const int64_t ow = take(B * Hq * 2 * a.N), oc = take(B * Hq), om = take(B * p.NCH * Hq), ol = take(B * p.NCH * Hq);
   const int64_t oo = take(B * p.NCH * Hq * a.D), og = take(B * p.n_mid_chunks * Hq * 2 * a.N);
-  const int64_t ov = take(B * p.n_rb * p.R * a.Mc_v);
   const int64_t oe = take(4);
   p.scratch_floats = o;
   float* s = reinterpret_cast<float*>(a.scratch);
   p.w = s + ow; p.cst = s + oc; p.m_part = s + om; p.l_part = s + ol; p.o_part = s + oo; p.g_part = s + og;
-  p.cv_part = s + ov;
   p.err = reinterpret_cast<int*>(s + oe);
   return FA_OK;
 }
@@ -1013,7 +996,7 @@ static int launch_decode(const DecodeParams& p, cudaStream_t st) {
   mark(0);
   if (a.n_mid > 0) {
     if ((rc = set_smem(decode_prepare_kernel<T>, p.smem_prepare)) != FA_OK) return rc;
-    dim3 g1(ceil_div(2 * a.N, PR_ROWS), a.B);
+    dim3 g1(ceil_div(2 * a.N, DEC_THREADS), a.Hkv, a.B);
     decode_prepare_kernel<T><<<g1, DEC_THREADS, p.smem_prepare, st>>>(p);
     FA_CHECK_LAUNCH("fa_decode_attn(prepare)");
   }
@@ -1034,17 +1017,12 @@ static int launch_decode(const DecodeParams& p, cudaStream_t st) {
   }
   FA_CHECK_LAUNCH("fa_decode_attn(main)");
   mark(2);
-  if (a.n_mid > 0) {
-    if ((rc = set_smem(decode_contract_kernel, p.smem_contract)) != FA_OK) return rc;
-    dim3 g3(p.n_rb, a.B);
-    decode_contract_kernel<<<g3, DEC_THREADS, p.smem_contract, st>>>(p);
-    FA_CHECK_LAUNCH("fa_decode_attn(contract)");
-  }
   mark(3);
   dim3 g4(a.Hq, a.B);
-  const int smem_out = (p.NCH + a.D) * 4;
-  decode_output_kernel<<<g4, 128, smem_out, st>>>(p);
-  FA_CHECK_LAUNCH("fa_decode_attn(output)");
+  const int smem_fin = finish_smem_bytes(p.NCH, a.n_mid > 0 ? a.N : 0, a.D);
+  if ((rc = set_smem(decode_finish_kernel, smem_fin)) != FA_OK) return rc;
+  decode_finish_kernel<<<g4, FIN_THREADS, smem_fin, st>>>(p);
+  FA_CHECK_LAUNCH("fa_decode_attn(finish)");
   mark(4);
   return FA_OK;
 }

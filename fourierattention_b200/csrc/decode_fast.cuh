@@ -275,7 +275,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars);   // full[0..2]
   volatile int* dead = reinterpret_cast<volatile int*>(bars + 6);
   // zero everything that is read but never (or only partly) written later
-  for (int e = tid; e < (L.qn - L.fnt_hi) / 16; e += FAST_T)
+  for (int e = tid; e < (L.smax - L.fnt_hi) / 16; e += FAST_T)
     reinterpret_cast<uint4*>(smem + L.fnt_hi)[e] = make_uint4(0u, 0u, 0u, 0u);
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) mbar_init(bars + i, 1);   // completed by expect_tx + the copied bytes
@@ -333,17 +333,15 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
     ph[n] = phase_mod((uint64_t)a.mid_l0 + (uint64_t)l0, (uint32_t)n, T_);
   }
   {
-    // block-diagonal verbatim-K query matrix, raw model-dtype values (the scale is applied to the fp32 sum)
+    // block-diagonal verbatim-K query matrix, raw model-dtype values (the scale is applied to the fp32
+    // sum); the zeros are already there, only the R x Mn_k entries inside the blocks are fetched
     const T* q = reinterpret_cast<const T*>(a.q) + (int64_t)b * a.q_sb;
-    const int w16 = qpitch - 8;
-    for (int e = tid; e < HN * w16; e += FAST_T) {
-      const int h = e / w16, col = e - h * w16;
-      T v = from_f32<T>(0.f);
-      if (h < Hq && col < Mn_k) {
-        const int g = h / R;
-        if (col >= a.kn_h[g] && col < a.kn_h[g + 1]) v = q[h * D + a.kn_list[col] - g * D];
-      }
-      qn[h * qpitch + col] = v;
+    for (int e = tid; e < R * Mn_k; e += FAST_T) {
+      const int r = e / Mn_k, col = e - r * Mn_k;
+      int g = 0;
+      while (g + 1 < a.Hkv && col >= a.kn_h[g + 1]) ++g;
+      const int h = g * R + r;
+      qn[h * qpitch + col] = q[h * D + a.kn_list[col] - g * D];
     }
   }
   for (int h = tid; h < HN; h += FAST_T) {

@@ -249,7 +249,7 @@ def decode_attn(q, k_sink, v_sink, k_win, v_win, k_mn, v_mn, k_coef, v_coef,
     if static_scratch:
         with torch.cuda.device(dev):
             check(lib.fa_decode_attn_static(C.byref(a), _stream(q)), "fa_decode_attn_static")
-        _count(4 if a.n_mid > 0 else 2)
+        _count(3 if a.n_mid > 0 else 2)
         return (out, m, l) if return_lse else out
     with torch.cuda.device(dev):
         nbytes = lib.fa_decode_scratch_bytes(C.byref(a))
@@ -259,7 +259,7 @@ def decode_attn(q, k_sink, v_sink, k_win, v_win, k_mn, v_mn, k_coef, v_coef,
         sc = scratch(dev, nbytes)
         a.scratch, a.scratch_bytes = sc.data_ptr(), sc.numel()
         check(lib.fa_decode_attn(C.byref(a), _stream(q)), "fa_decode_attn")
-    _count(4 if a.n_mid > 0 else 2)
+    _count(3 if a.n_mid > 0 else 2)
     return (out, m, l) if return_lse else out
 
 
