@@ -329,8 +329,8 @@ def ours_arm(args, w):
         step_bytes = op_bytes * B * L
         # DRAM read+write bytes of one launch from the committed ncu capture of `profile_small`, whose launches
         # have this workload's per-launch shape: 303.7 MB measured against 294.1 MB algorithmic.
-        fast = ops.last_decode_path == 1
-        kernel_name = "decode_main_fast_kernel" if fast else "decode_main_kernel"
+        fast = ops.last_decode_path in (1, 2)
+        kernel_name = {0: "decode_main_kernel", 1: "decode_main_fast_kernel", 2: "decode_main_ws_kernel"}[ops.last_decode_path]
         traffic, traffic_src = None, None
         if fast and world == 1 and args.workload in ("llama31_8b_32k", "profile_small"):
             traffic = 303.7e6

@@ -42,6 +42,7 @@ class DecodeArgs(C.Structure):
         ("out", vp), ("m_out", vp), ("l_out", vp),
         ("scratch", vp), ("scratch_bytes", sz),
         ("phase_events_host", vp),
+        ("kn_h_host", vp), ("vn_h_host", vp),
     ]
 
 

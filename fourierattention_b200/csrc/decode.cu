@@ -700,6 +700,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) decode_main_kernel(const __gri
 
 #include "decode_fast.cuh"
 
+#include "decode_ws.cuh"
+
 constexpr int FAST_THREADS = FAST_T;
 
 template <typename T, int NT, int NH>
@@ -717,8 +719,29 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) decode_main_fast_kernel(const
   }
 #ifdef FA_PHASE_TIMING
   if (threadIdx.x == 0)
-    atomicAdd(&g_phase_clk[(int)blockIdx.x < p.n_il_chunks ? 12 : 13], (unsigned long long)(clock64() - cta_t0));
+    atomicAdd(&g_phase_clk[(int)blockIdx.x < p.n_il_chunks ? 14 : 15], (unsigned long long)(clock64() - cta_t0));
 #endif
+}
+
+template <typename T>
+__global__ void __launch_bounds__(WS_T, 1) decode_main_ws_kernel(const __grid_constant__ DecodeParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const int b = blockIdx.y;
+#ifdef FA_PHASE_TIMING
+  const long long cta_t0 = clock64();
+#endif
+  if ((int)blockIdx.x < p.n_il_chunks) {
+    if (threadIdx.x >= DEC_THREADS) return;   // the sinks+window pass is written for 256 threads
+    il_chunk<T>(p, b, blockIdx.x, smem_raw);
+#ifdef FA_PHASE_TIMING
+    if (threadIdx.x == 0) atomicAdd(&g_phase_clk[14], (unsigned long long)(clock64() - cta_t0));
+#endif
+  } else {
+    mid_chunk_ws<T>(p, b, blockIdx.x - p.n_il_chunks, smem_raw);
+#ifdef FA_PHASE_TIMING
+    if (threadIdx.x == 256) atomicAdd(&g_phase_clk[15], (unsigned long long)(clock64() - cta_t0));
+#endif
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -945,10 +968,49 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
           mid_smem_bytes = L.total;
         }
       }
+      // warp-specialised form: 128-token super-tiles, and every 8-head column tile must find its
+      // verbatim columns inside WS_KS (K) and WS_MTV (V) 16-column tiles, which only the host copies
+      // of the offset tables can tell
+      if (p.fast && NH == 2 && a.kn_h_host && a.vn_h_host && getenv("FA_DECODE_NO_WS") == nullptr) {
+        bool ok = true;
+        for (int nt = 0; nt < NT && ok; ++nt) {
+          const int g0 = (8 * nt) / p.R, last = (a.Hq < 8 * nt + 8 ? a.Hq : 8 * nt + 8) - 1, g1 = last / p.R;
+          const int kc0 = a.kn_h_host[g0] & ~15, kc1 = (a.kn_h_host[g1 + 1] + 15) & ~15;
+          const int mtv0 = a.vn_h_host[g0] >> 4, mtvn = ((a.vn_h_host[g1 + 1] + 15) >> 4) - mtv0;
+          if ((kc1 - kc0) / 16 > WS_KS || mtvn > WS_MTV) ok = false;
+        }
+        const WsSmem L = ws_smem(a.N, a.Mn_k, a.Mn_v);
+        if (ok && L.total <= 227 * 1024) {
+          p.fast = 2;
+          mid_smem_bytes = L.total;
+        }
+      }
     }
     const int sms = sm_count();
-    int target = ((p.fast ? 1 : 3) * sms) / (a.B * p.n_groups) - p.n_il_chunks;
     const int max_chunks = ceil_div(a.n_mid, J);
+    if (p.fast && p.n_il > 0) {
+      // One wave of CTAs per launch.  Split the CTAs of a sequence between sinks+window rows and the
+      // middle span so that the slowest CTA is as short as possible; measured costs on B200 in clock
+      // ticks: 870 per sinks+window row (CUDA cores), 24 K set-up + 142 per middle-span token.
+      const int per_seq = sms / a.B > 2 ? sms / a.B : 2;
+      double best = 1e30;
+      int best_il = 1;
+      for (int n_il = 1; n_il < per_seq; ++n_il) {
+        const int il_rows = rup(ceil_div(p.n_il, n_il), TR);
+        int n_mid = per_seq - ceil_div(p.n_il, il_rows);
+        if (n_mid > max_chunks) n_mid = max_chunks;
+        const int mid_tok = rup(ceil_div(a.n_mid, n_mid), J);
+        const double t_il = 870.0 * il_rows, t_mid = 24000.0 + 142.0 * mid_tok;
+        const double t = t_il > t_mid ? t_il : t_mid;
+        if (t < best) {
+          best = t;
+          best_il = n_il;
+        }
+      }
+      p.il_chunk_rows = rup(ceil_div(p.n_il, best_il), TR);
+      p.n_il_chunks = ceil_div(p.n_il, p.il_chunk_rows);
+    }
+    int target = ((p.fast ? 1 : 3) * sms) / (a.B * p.n_groups) - p.n_il_chunks;
     if (target < 1) target = 1;
     if (target > max_chunks) target = max_chunks;
     p.mid_chunk = rup(ceil_div(a.n_mid, target), J);
@@ -1002,7 +1064,10 @@ static int launch_decode(const DecodeParams& p, cudaStream_t st) {
   }
   mark(1);
   dim3 g2(p.n_il_chunks + p.n_mid_chunks * p.n_groups, a.B);
-  if (p.fast) {
+  if (p.fast == 2) {
+    if ((rc = set_smem(decode_main_ws_kernel<T>, p.smem_main)) != FA_OK) return rc;
+    decode_main_ws_kernel<T><<<g2, WS_T, p.smem_main, st>>>(p);
+  } else if (p.fast) {
 #define FA_FAST_CASE(NT_, NH_)                                                                   \
   if (p.fNT == NT_ && p.fNH == NH_) {                                                            \
     if ((rc = set_smem(decode_main_fast_kernel<T, NT_, NH_>, p.smem_main)) != FA_OK) return rc;  \
@@ -1075,7 +1140,7 @@ extern "C" int fa_decode_path(const fa_decode_args_t* args) {
   a.scratch = nullptr;
   int rc = make_plan(a, p);
   if (rc != FA_OK) return rc;
-  return (a.n_mid > 0 && p.fast) ? 1 : 0;
+  return a.n_mid > 0 ? p.fast : 0;
 }
 
 extern "C" int fa_decode_attn(const fa_decode_args_t* args, fa_stream_t stream) {

@@ -1,0 +1,706 @@
+// Warp-specialised form of the tensor-core middle-span pass.  Included by decode.cu after
+// decode_fast.cuh (same namespace, same MMA / TMA primitives, same mathematics).
+//
+// decode_fast.cuh runs the phases of a super-tile one after another on all warps, so every phase
+// exposes its own latency.  Here the 16 warps of a CTA split into two groups that work on different
+// super-tiles at the same time:
+//
+//   spectral warps (0..7)   node basis of super-tile j (rotation of a fixed table) and the node
+//                           scores  s_node = Fn_t * w  (w stays in registers as MMA fragments);
+//                           they run up to two super-tiles ahead of the score warps
+//   score warps (8..15)     warp = (8-head column tile nt, 64-token half): interpolation of the node
+//                           scores, verbatim-K scores, softmax, projection of the probabilities onto
+//                           the nodes, verbatim-V numerators; then all eight add the projected
+//                           probabilities to g (each owns 16-row tiles of the 2N rows)
+//
+// Hand-offs are mbarriers with bounded waits (node scores + basis: full/empty per buffer; K/V half
+// tiles: full/empty per ring slot); the two halves of a column tile agree on the running maximum
+// through a 64-thread named barrier, and the score warps meet once per super-tile before the g update.
+// The score warps refill the ring themselves: the nt = 0 warp of a half waits until the other warps
+// of that half have released the slot and issues the TMA boxes of the tile three places ahead.
+// Registers move with the work: the spectral warps give up registers (setmaxnreg) that the score
+// warps, which hold the g and verbatim-V accumulators, take over.
+//
+// The node set is symmetric about the centre of the super-tile, so the basis table holds the eight
+// nodes right of the centre only and the rotation is taken at the centre (a half-integer position:
+// phases are kept modulo 2T).
+#pragma once
+
+constexpr int WS_MTV = 4;   // 16-column tiles of verbatim V a score warp owns
+constexpr int WS_KS = 4;    // 16-column steps of verbatim K a score warp contracts
+constexpr int WS_T = 512;
+constexpr int WS_SREG = 104, WS_QREG = 152;   // registers per thread of the two groups (sum = 2 x 128)
+
+#ifdef FA_PHASE_TIMING
+#define WS_TICK(i)                                                      \
+  do {                                                                  \
+    if (ticker__) {                                                     \
+      const long long now__ = clock64();                                \
+      atomicAdd(&g_phase_clk[i], (unsigned long long)(now__ - tick__)); \
+      tick__ = now__;                                                   \
+    }                                                                   \
+  } while (0)
+#else
+#define WS_TICK(i)
+#endif
+
+struct WsSmem {
+  int ec, es, fnt, interp_hi, interp_lo, snode32, snode, pw, ptx, ptp, alpha, mx, lx, bars, slots, total;
+  int fpitch, kpad, slot_bytes;
+};
+__host__ __device__ inline WsSmem ws_smem(int N, int Mn_k, int Mn_v) {
+  WsSmem s;
+  int o = 0;
+  auto take = [&](int bytes) {
+    int r = o;
+    o += (bytes + 15) / 16 * 16;
+    return r;
+  };
+  s.kpad = (2 * N + 15) / 16 * 16;
+  s.fpitch = s.kpad + 8;
+  s.ec = take(8 * N * 4);
+  s.es = take(8 * N * 4);
+  s.fnt = take(2 * 2 * FD * s.fpitch * 2);    // [buffer][hi, lo][node][fpitch]
+  s.interp_hi = take(128 * 24 * 2);
+  s.interp_lo = take(128 * 24 * 2);
+  s.snode32 = take(2 * FD * 32 * 4);          // partial node scores of the two halves of the 2N rows
+  s.snode = take(2 * 2 * 32 * 24 * 2);        // [buffer][hi, lo][head][24]
+  s.pw = take(8 * 8 * 72 * 2);                // per score warp: probabilities [8 heads][64 tokens + 8]
+  s.ptx = take(2 * 2 * 32 * 24 * 2);          // [buffer][hi, lo][head][24]  probabilities on the nodes
+  s.ptp = take(4 * FD * 8 * 4);               // second half's contribution to them, per column tile
+  s.alpha = take(2 * 32 * 4);
+  s.mx = take(4 * 2 * 8 * 4);
+  s.lx = take(4 * 8 * 4);
+  s.bars = take(16 * 8);
+  const int mnk16 = (Mn_k + 15) / 16 * 16, mnv16 = (Mn_v + 15) / 16 * 16;
+  const int w = mnk16 > mnv16 ? mnk16 : mnv16;
+  const int boxes = (w + 63) / 64 > 0 ? (w + 63) / 64 : 1;
+  s.slot_bytes = boxes * 8192;
+  o = (o + 1023) / 1024 * 1024;
+  s.slots = take(3 * s.slot_bytes);
+  s.total = o;
+  return s;
+}
+
+__device__ __forceinline__ void ws_group_sync(int id) { asm volatile("bar.sync %0, 256;\n" ::"r"(id) : "memory"); }
+__device__ __forceinline__ void ws_pair_sync(int id) { asm volatile("bar.sync %0, 64;\n" ::"r"(id) : "memory"); }
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair(T a, T b) {
+  const uint16_t lo = *reinterpret_cast<uint16_t*>(&a), hi = *reinterpret_cast<uint16_t*>(&b);
+  return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+
+template <typename T>
+__device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned char* smem) {
+  constexpr int J = 128, HN = 32;
+  constexpr bool kBf16 = !std::is_same<T, __half>::value;
+  const fa_decode_args_t& a = p.a;
+  const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+  const int gq = lane >> 2, tq = lane & 3;
+  const int N = a.N, D = a.D, R = p.R, Hq = a.Hq, Mn_k = a.Mn_k, Mn_v = a.Mn_v;
+  const int NT = p.fNT;
+  const uint32_t T2 = 2u * (uint32_t)a.T;
+  const float inv_T = 1.0f / (float)a.T;
+  const WsSmem L = ws_smem(N, Mn_k, Mn_v);
+  float* ec = reinterpret_cast<float*>(smem + L.ec);
+  float* es = reinterpret_cast<float*>(smem + L.es);
+  __half* fnt = reinterpret_cast<__half*>(smem + L.fnt);
+  __half* interp_hi = reinterpret_cast<__half*>(smem + L.interp_hi);
+  __half* interp_lo = reinterpret_cast<__half*>(smem + L.interp_lo);
+  float* snode32 = reinterpret_cast<float*>(smem + L.snode32);
+  __half* snode = reinterpret_cast<__half*>(smem + L.snode);
+  __half* ptx = reinterpret_cast<__half*>(smem + L.ptx);
+  float* ptp = reinterpret_cast<float*>(smem + L.ptp);
+  float* alpha = reinterpret_cast<float*>(smem + L.alpha);
+  float* mx = reinterpret_cast<float*>(smem + L.mx);
+  float* lx = reinterpret_cast<float*>(smem + L.lx);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars);
+  uint64_t* full_slot = bars;         // [3] a K or V half tile has landed
+  uint64_t* empty_slot = bars + 3;    // [3] the score warps of its half are done with it
+  uint64_t* full_sp = bars + 6;       // [2] node basis + node scores of a super-tile are written
+  uint64_t* empty_sp = bars + 8;      // [2] ... and no longer needed
+  volatile int* dead = reinterpret_cast<volatile int*>(bars + 10);
+  unsigned char* slots = smem + L.slots;
+  const int fpitch = L.fpitch, kpad = L.kpad;
+  const int ktot = kpad / 16;
+
+  const int l0 = chunk * p.mid_chunk;
+  const int l1 = min(a.n_mid, l0 + p.mid_chunk);
+  const int nst = (l1 - l0 + J - 1) / J;
+  const int n_tiles = 4 * nst;   // per super-tile: K half 0, K half 1, V half 0, V half 1
+  const int nbK = (Mn_k + 63) / 64, nbV = (Mn_v + 63) / 64;
+  const int64_t slot_id = (int64_t)b * p.NCH + p.n_il_chunks + chunk;
+
+  // called by a whole warp: request half tile i into ring slot i % 3
+  auto issue_tile = [&](int i) {
+    if (i >= n_tiles) return;
+    const int s = i % 3, r = i & 3;
+    const int lf = l0 + (i >> 2) * J + (r & 1) * FH;
+    const bool is_v = r >= 2;
+    const int nb = is_v ? nbV : nbK;
+    if (lane == 0) mbar_expect_tx(full_slot + s, (uint32_t)nb * 8192u);
+    __syncwarp();
+    if (lane < nb) tma_box(slots + s * L.slot_bytes + lane * 8192, is_v ? &p.tm_v : &p.tm_k, 64 * lane, lf, b, full_slot + s);
+  };
+
+  // ---- set-up (all warps) ---------------------------------------------------------------------
+  if (tid == 0) {
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(full_slot + i, 1);
+      mbar_init(empty_slot + i, NT);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(full_sp + i, 8);
+      mbar_init(empty_sp + i, 8);
+    }
+    *dead = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  for (int e = tid; e < 2 * FD * 32; e += WS_T) snode32[e] = 0.f;
+  __syncthreads();
+  if (wp == 8) {
+    if (lane == 0) {
+      if (nbK) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&p.tm_k) : "memory");
+      if (nbV) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&p.tm_v) : "memory");
+    }
+    for (int i = 0; i < 3; ++i) issue_tile(i);
+  }
+  for (int e = tid; e < 8 * N; e += WS_T) {
+    const int k = e / N, n = e - k * N;
+    // node 8+k lies (2 x_k - 127) / 2 tokens right of the centre
+    const uint32_t ph = phase_mod((uint64_t)(2 * c_nodes128[8 + k] - (J - 1)), (uint32_t)n, T2);
+    float s, c;
+    sincospif((float)ph * inv_T, &s, &c);
+    ec[e] = c;
+    es[e] = s;
+  }
+  for (int e = tid; e < J * FD; e += WS_T) {
+    const int j = e / FD, k = e - j * FD;
+    __half hi, lo;
+    split_h(g_interp128[e], hi, lo);
+    interp_hi[j * 24 + k] = hi;
+    interp_lo[j * 24 + k] = lo;
+  }
+  __syncthreads();
+
+  if (wp < 8) {
+    // =========================== spectral warps ================================================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(WS_SREG));
+#ifdef FA_PHASE_TIMING
+    const bool ticker__ = false;
+    long long tick__ = clock64();
+#endif
+    const int nt1 = wp & 3, khalf = wp >> 2;
+    // this chunk's verbatim-V partial starts from zero (the score warps add into it at the end)
+    {
+      float* ob = p.o_part + slot_id * Hq * D;
+      for (int e = tid; e < Hq * D; e += 256) ob[e] = 0.f;
+    }
+    // w as persistent B fragments (hi / lo): k = frequency row, n = head; this warp holds column
+    // tile nt1 for half `khalf` of the 2N rows
+    constexpr int KH = 16;
+    const int kh_steps = (ktot + 1) / 2;
+    uint32_t bhi[KH][2], blo[KH][2];
+    {
+      const float* wb = p.w + (int64_t)b * Hq * 2 * N;
+      const int h = 8 * nt1 + gq;
+#pragma unroll
+      for (int i = 0; i < KH; ++i) {
+        const int k0 = 16 * (khalf * kh_steps + i);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int k = k0 + 2 * tq + 8 * r;
+          float v0 = 0.f, v1 = 0.f;
+          if (nt1 < NT && i < kh_steps && h < Hq && k < 2 * N) {
+            v0 = wb[(int64_t)h * 2 * N + k];
+            v1 = wb[(int64_t)h * 2 * N + k + 1];
+          }
+          __half h0, l0_, h1, l1_;
+          split_h(v0, h0, l0_);
+          split_h(v1, h1, l1_);
+          __half2 hh = __halves2half2(h0, h1), ll = __halves2half2(l0_, l1_);
+          bhi[i][r] = *reinterpret_cast<uint32_t*>(&hh);
+          blo[i][r] = *reinterpret_cast<uint32_t*>(&ll);
+        }
+      }
+    }
+    // phases (modulo 2T) of this thread's two frequencies at the centre of the first super-tile
+    const int np = tid & 127, kk = tid >> 7;
+    uint32_t ph2[2], d2[2];
+#pragma unroll
+    for (int f = 0; f < 2; ++f) {
+      const uint32_t n = (uint32_t)(2 * np + f);
+      const uint64_t centre2 = 2ull * ((uint64_t)a.mid_l0 + (uint64_t)l0) + (uint64_t)(J - 1);
+      ph2[f] = phase_mod(centre2 % (uint64_t)T2, n, T2);
+      d2[f] = phase_mod((uint64_t)(2 * J), n, T2);
+    }
+    WS_TICK(10);
+    for (int j = 0; j < nst; ++j) {
+      const int buf = j & 1;
+      __half* fh = fnt + (buf * 2 + 0) * FD * fpitch;
+      __half* fl = fnt + (buf * 2 + 1) * FD * fpitch;
+      if (j >= 2) mbar_wait(empty_sp + buf, ((j >> 1) - 1) & 1, dead, p.err);
+      WS_TICK(10);
+      // ---- node basis: rotate the table to this super-tile's centre ------------------------------
+      if (2 * np < N) {
+        float rc[2], rs[2];
+#pragma unroll
+        for (int f = 0; f < 2; ++f) {
+          sincospif((float)ph2[f] * inv_T, &rs[f], &rc[f]);
+          ph2[f] += d2[f];
+          if (ph2[f] >= T2) ph2[f] -= T2;
+        }
+        auto put = [&](int k, float c0, float c1, float s0, float s1) {
+          const __half2 ch = __floats2half2_rn(c0, c1), sh = __floats2half2_rn(s0, s1);
+          const float2 chf = __half22float2(ch), shf = __half22float2(sh);
+          const __half2 cl = __floats2half2_rn(c0 - chf.x, c1 - chf.y), sl = __floats2half2_rn(s0 - shf.x, s1 - shf.y);
+          *reinterpret_cast<__half2*>(fh + k * fpitch + 2 * np) = ch;
+          *reinterpret_cast<__half2*>(fl + k * fpitch + 2 * np) = cl;
+          *reinterpret_cast<__half2*>(fh + k * fpitch + N + 2 * np) = sh;
+          *reinterpret_cast<__half2*>(fl + k * fpitch + N + 2 * np) = sl;
+        };
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int kp = kk * 4 + i;
+          const float2 e_c = *reinterpret_cast<const float2*>(ec + kp * N + 2 * np);
+          const float2 e_s = *reinterpret_cast<const float2*>(es + kp * N + 2 * np);
+          const float t1a = rc[0] * e_c.x, t2a = rs[0] * e_s.x, t3a = rs[0] * e_c.x, t4a = rc[0] * e_s.x;
+          const float t1b = rc[1] * e_c.y, t2b = rs[1] * e_s.y, t3b = rs[1] * e_c.y, t4b = rc[1] * e_s.y;
+          put(8 + kp, t1a - t2a, t1b - t2b, t3a + t4a, t3b + t4b);   // centre + d
+          put(7 - kp, t1a + t2a, t1b + t2b, t3a - t4a, t3b - t4b);   // centre - d
+        }
+      }
+      ws_group_sync(1);
+      WS_TICK(11);
+      // ---- scores at the nodes: s_node[16 x HN] = Fn_t[16 x 2N] * w[2N x HN] -----------------------
+      if (nt1 < NT) {
+        float acc[4][4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[c][e] = 0.f;
+#pragma unroll
+        for (int i = 0; i < KH; ++i) {
+          const int ks = khalf * kh_steps + i;
+          if (i < kh_steps && ks < ktot) {
+            uint32_t ah[4], al[4];
+            const int off = lds_a_row(lane) * fpitch + 16 * ks + lds_a_col(lane);
+            ldsm_x4(ah, fh + off);
+            ldsm_x4(al, fl + off);
+            mma16816<__half>(acc[i & 3], ah, bhi[i]);
+            mma16816<__half>(acc[i & 3], al, bhi[i]);
+            mma16816<__half>(acc[i & 3], ah, blo[i]);
+          }
+        }
+        float* red = snode32 + khalf * (FD * HN);
+        const int col = 8 * nt1 + 2 * tq;
+        red[gq * HN + col] = (acc[0][0] + acc[1][0]) + (acc[2][0] + acc[3][0]);
+        red[gq * HN + col + 1] = (acc[0][1] + acc[1][1]) + (acc[2][1] + acc[3][1]);
+        red[(gq + 8) * HN + col] = (acc[0][2] + acc[1][2]) + (acc[2][2] + acc[3][2]);
+        red[(gq + 8) * HN + col + 1] = (acc[0][3] + acc[1][3]) + (acc[2][3] + acc[3][3]);
+      }
+      ws_group_sync(1);
+      WS_TICK(12);
+      {
+        __half* sh_ = snode + (buf * 2 + 0) * 32 * 24;
+        __half* sl_ = snode + (buf * 2 + 1) * 32 * 24;
+        for (int e = tid; e < FD * HN; e += 256) {
+          const int k = e / HN, h = e - k * HN;
+          __half hi, lo;
+          split_h(snode32[e] + snode32[FD * HN + e], hi, lo);
+          sh_[h * 24 + k] = hi;
+          sl_[h * 24 + k] = lo;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_sp + buf);
+      WS_TICK(13);
+    }
+    __syncthreads();
+    return;
+  }
+
+  // ============================= score warps ======================================================
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(WS_QREG));
+#ifdef FA_PHASE_TIMING
+  const bool ticker__ = (tid == 256);
+  long long tick__ = clock64();
+#endif
+  const int qw = wp - 8, nt = qw & 3, half = qw >> 2;
+  const bool act = nt < NT;
+  __half* pw16 = reinterpret_cast<__half*>(smem + L.pw) + qw * 8 * 72;   // this warp's probabilities
+  T* pwT = reinterpret_cast<T*>(pw16);
+  // column ranges of this warp's heads in the verbatim stores
+  int kc0 = 0, kc1 = 0, mtv0 = 0, mtvn = 0;
+  if (act) {
+    const int g0 = (8 * nt) / R, g1 = (min(Hq, 8 * nt + 8) - 1) / R;
+    kc0 = a.kn_h[g0] & ~15;
+    kc1 = (a.kn_h[g1 + 1] + 15) & ~15;
+    mtv0 = a.vn_h[g0] >> 4;
+    mtvn = ((a.vn_h[g1 + 1] + 15) >> 4) - mtv0;
+  }
+  // the heads' verbatim-K query entries as MMA B fragments (raw model-dtype values; the softmax
+  // scale is applied to the fp32 sums)
+  uint32_t bq[WS_KS][2];
+  {
+    const T* q = reinterpret_cast<const T*>(a.q) + (int64_t)b * a.q_sb;
+    const int h = 8 * nt + gq;
+    const int g = h / R;
+    int c_lo = 0, c_hi = 0;
+    if (act && h < Hq) {
+      c_lo = a.kn_h[g];
+      c_hi = a.kn_h[g + 1];
+    }
+#pragma unroll
+    for (int ks = 0; ks < WS_KS; ++ks) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int col = kc0 + 16 * ks + 2 * tq + 8 * r;
+        T v0 = from_f32<T>(0.f), v1 = from_f32<T>(0.f);
+        if (col >= c_lo && col < c_hi) v0 = q[h * D + a.kn_list[col] - g * D];
+        if (col + 1 >= c_lo && col + 1 < c_hi) v1 = q[h * D + a.kn_list[col + 1] - g * D];
+        bq[ks][r] = pack_pair<T>(v0, v1);
+      }
+    }
+  }
+  const int hc0 = 8 * nt + 2 * tq;   // this thread's two head columns
+  const float cst0 = (act && hc0 < Hq) ? p.cst[(int64_t)b * Hq + hc0] : 0.f;
+  const float cst1 = (act && hc0 + 1 < Hq) ? p.cst[(int64_t)b * Hq + hc0 + 1] : 0.f;
+  float m_run0 = NEG_BIG, m_run1 = NEG_BIG, lsum0 = 0.f, lsum1 = 0.f;
+  float Gacc[4][4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) Gacc[i][n][e] = 0.f;
+  float Oacc[WS_MTV][4];
+#pragma unroll
+  for (int i = 0; i < WS_MTV; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) Oacc[i][e] = 0.f;
+  WS_TICK(0);
+
+  for (int st = 0; st < nst; ++st) {
+    const int buf = st & 1;
+    const int tok0 = l0 + st * J + half * FH;   // first token of this warp's half
+    const __half* fh = fnt + (buf * 2 + 0) * FD * fpitch;
+    const __half* fl = fnt + (buf * 2 + 1) * FD * fpitch;
+    mbar_wait(full_sp + buf, (st >> 1) & 1, dead, p.err);
+    WS_TICK(0);
+    float sc[4][4];
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sc[mt][e] = 0.f;
+    const int iK = 4 * st + half, sK = iK % 3;
+    const uint32_t parK = (uint32_t)(iK / 3) & 1u;
+    if (act) {
+      // ---- interpolate the node scores to this warp's 64 tokens ---------------------------------
+      uint32_t bh[2], bl[2];
+      const int boff = (8 * nt + lds_b_row(lane)) * 24 + lds_b_col(lane);
+      ldsm_x2(bh, snode + (buf * 2 + 0) * 32 * 24 + boff);
+      ldsm_x2(bl, snode + (buf * 2 + 1) * 32 * 24 + boff);
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        uint32_t ah[4], al[4];
+        const int off = (half * FH + 16 * mt + lds_a_row(lane)) * 24 + lds_a_col(lane);
+        ldsm_x4(ah, interp_hi + off);
+        ldsm_x4(al, interp_lo + off);
+        mma16816<__half>(sc[mt], ah, bh);
+        mma16816<__half>(sc[mt], al, bh);
+        mma16816<__half>(sc[mt], ah, bl);
+      }
+      WS_TICK(1);
+      // ---- verbatim-dim scores from the K rows ---------------------------------------------------
+      mbar_wait(full_slot + sK, parK, dead, p.err);
+      WS_TICK(2);
+      const unsigned char* ks_ = slots + sK * L.slot_bytes;
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        float vb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < WS_KS; ++ks) {
+          const int c = kc0 + 16 * ks;
+          if (c < kc1) {
+            uint32_t af[4];
+            ldsm_x4(af, ks_ + sw_off(16 * mt + lds_a_row(lane), (c + lds_a_col(lane)) >> 3));
+            mma16816<T>(vb, af, bq[ks]);
+          }
+        }
+        sc[mt][0] += p.c2 * vb[0] + cst0;
+        sc[mt][1] += p.c2 * vb[1] + cst1;
+        sc[mt][2] += p.c2 * vb[2] + cst0;
+        sc[mt][3] += p.c2 * vb[3] + cst1;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_slot + sK);
+    }
+    WS_TICK(3);
+    if (nt == 0) {   // refill the slot once every warp of this half has released it
+      mbar_wait(empty_slot + sK, parK, dead, p.err);
+      WS_TICK(10);
+      issue_tile(iK + 3);
+      WS_TICK(11);
+    }
+    // ---- softmax over the 128 tokens of the super-tile (both halves agree on the maximum) ----------
+    float al0 = 1.f, al1 = 1.f;
+    float pf[4][4];   // probabilities, already rounded to fp16
+    float pt_acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const int iV = 4 * st + 2 + half, sV = iV % 3;
+    const uint32_t parV = (uint32_t)(iV / 3) & 1u;
+    if (act) {
+      float mx0 = NEG_BIG, mx1 = NEG_BIG;
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        const bool ok0 = (tok0 + 16 * mt + gq) < l1, ok1 = (tok0 + 16 * mt + gq + 8) < l1;
+        mx0 = fmaxf(mx0, fmaxf(ok0 ? sc[mt][0] : NEG_BIG, ok1 ? sc[mt][2] : NEG_BIG));
+        mx1 = fmaxf(mx1, fmaxf(ok0 ? sc[mt][1] : NEG_BIG, ok1 ? sc[mt][3] : NEG_BIG));
+      }
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+      }
+      if (gq == 0) {
+        mx[(nt * 2 + half) * 8 + 2 * tq] = mx0;
+        mx[(nt * 2 + half) * 8 + 2 * tq + 1] = mx1;
+      }
+      ws_pair_sync(2 + nt);
+      const float mn0 = fmaxf(m_run0, fmaxf(mx0, mx[(nt * 2 + (half ^ 1)) * 8 + 2 * tq]));
+      const float mn1 = fmaxf(m_run1, fmaxf(mx1, mx[(nt * 2 + (half ^ 1)) * 8 + 2 * tq + 1]));
+      al0 = exp2f(m_run0 - mn0);
+      al1 = exp2f(m_run1 - mn1);
+      m_run0 = mn0;
+      m_run1 = mn1;
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        const bool ok0 = (tok0 + 16 * mt + gq) < l1, ok1 = (tok0 + 16 * mt + gq + 8) < l1;
+        const __half h0 = __float2half_rn(ok0 ? exp2f(sc[mt][0] - mn0) : 0.f);
+        const __half h1 = __float2half_rn(ok0 ? exp2f(sc[mt][1] - mn1) : 0.f);
+        const __half h2 = __float2half_rn(ok1 ? exp2f(sc[mt][2] - mn0) : 0.f);
+        const __half h3 = __float2half_rn(ok1 ? exp2f(sc[mt][3] - mn1) : 0.f);
+        // B-operand layout [head][token]; the sums use the rounded values
+        const int j0 = 16 * mt + gq;
+        pw16[(2 * tq) * 72 + j0] = h0;
+        pw16[(2 * tq + 1) * 72 + j0] = h1;
+        pw16[(2 * tq) * 72 + j0 + 8] = h2;
+        pw16[(2 * tq + 1) * 72 + j0 + 8] = h3;
+        pf[mt][0] = __half2float(h0);
+        pf[mt][1] = __half2float(h1);
+        pf[mt][2] = __half2float(h2);
+        pf[mt][3] = __half2float(h3);
+        s0 += pf[mt][0] + pf[mt][2];
+        s1 += pf[mt][1] + pf[mt][3];
+      }
+      lsum0 = lsum0 * al0 + s0;   // this thread's rows only; the lanes are added at the end
+      lsum1 = lsum1 * al1 + s1;
+      __syncwarp();
+      WS_TICK(4);
+      // ---- project the probabilities onto the nodes: pt[16 x 8] = Interp^T[16 x 64] * P[64 x 8] ------
+      uint32_t bp[4][2];
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) ldsm_x2(bp[ks], pw16 + lds_b_row(lane) * 72 + 16 * ks + lds_b_col(lane));
+      {
+        float pt2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          uint32_t af[4], al_[4];
+          const int ioff = (half * FH + 16 * ks + lds_at_row(lane)) * 24 + lds_at_col(lane);
+          ldsm_x4_t(af, interp_hi + ioff);
+          ldsm_x4_t(al_, interp_lo + ioff);
+          mma16816<__half>(pt_acc, af, bp[ks]);
+          mma16816<__half>(pt2, al_, bp[ks]);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) pt_acc[e] += pt2[e];
+      }
+      WS_TICK(5);
+      // ---- verbatim-V numerators -------------------------------------------------------------------
+      uint32_t bp_lo[4][2];
+      if (kBf16) {
+        // an fp16 value splits exactly into two bf16 values, so the verbatim-V GEMM (model dtype)
+        // sees the same probabilities as the spectral side and the denominator
+        __syncwarp();
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            pwT[(2 * tq + (e & 1)) * 72 + 16 * mt + gq + 8 * (e >> 1)] = from_f32<T>(pf[mt][e]);
+        __syncwarp();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) ldsm_x2(bp[ks], pwT + lds_b_row(lane) * 72 + 16 * ks + lds_b_col(lane));
+        __syncwarp();
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float hi = to_f32(from_f32<T>(pf[mt][e]));
+            pwT[(2 * tq + (e & 1)) * 72 + 16 * mt + gq + 8 * (e >> 1)] = from_f32<T>(pf[mt][e] - hi);
+          }
+        __syncwarp();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) ldsm_x2(bp_lo[ks], pwT + lds_b_row(lane) * 72 + 16 * ks + lds_b_col(lane));
+      }
+      mbar_wait(full_slot + sV, parV, dead, p.err);
+      WS_TICK(6);
+      const unsigned char* vs_ = slots + sV * L.slot_bytes;
+#pragma unroll
+      for (int i = 0; i < WS_MTV; ++i) {
+        Oacc[i][0] *= al0;
+        Oacc[i][1] *= al1;
+        Oacc[i][2] *= al0;
+        Oacc[i][3] *= al1;
+        if (i < mtvn) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            uint32_t af[4];
+            ldsm_x4_t(af, vs_ + sw_off(16 * ks + lds_at_row(lane), (16 * (mtv0 + i) + lds_at_col(lane)) >> 3));
+            mma16816<T>(Oacc[i], af, bp[ks]);
+            if (kBf16) mma16816<T>(Oacc[i], af, bp_lo[ks]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_slot + sV);
+    }
+    WS_TICK(7);
+    if (nt == 0) {
+      mbar_wait(empty_slot + sV, parV, dead, p.err);
+      WS_TICK(12);
+      issue_tile(iV + 3);
+      WS_TICK(13);
+    }
+    // ---- hand the node-projected probabilities of the column tile to every score warp -------------
+    if (act) {
+      if (half == 1) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ptp[nt * FD * 8 + (gq + 8 * (e >> 1)) * 8 + 2 * tq + (e & 1)] = pt_acc[e];
+      }
+      ws_pair_sync(2 + nt);
+      if (half == 0) {
+        __half* ph_ = ptx + (buf * 2 + 0) * 32 * 24;
+        __half* pl_ = ptx + (buf * 2 + 1) * 32 * 24;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float v = pt_acc[e] + ptp[nt * FD * 8 + (gq + 8 * (e >> 1)) * 8 + 2 * tq + (e & 1)];
+          __half hi, lo;
+          split_h(v, hi, lo);
+          const int o = (hc0 + (e & 1)) * 24 + gq + 8 * (e >> 1);
+          ph_[o] = hi;
+          pl_[o] = lo;
+        }
+        if (gq == 0) {
+          alpha[buf * 32 + hc0] = al0;
+          alpha[buf * 32 + hc0 + 1] = al1;
+        }
+      }
+    }
+    ws_group_sync(7);
+    WS_TICK(8);
+    // ---- g[2N x HN] += Fn_t^T[2N x 16] * pt[16 x HN]  (this warp's 16-row tiles) -------------------
+    {
+      uint32_t bf[4][2], bl[4][2];
+      float ap[4][2];
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        if (n < NT) {
+          const int o = (8 * n + lds_b_row(lane)) * 24 + lds_b_col(lane);
+          ldsm_x2(bf[n], ptx + (buf * 2 + 0) * 32 * 24 + o);
+          ldsm_x2(bl[n], ptx + (buf * 2 + 1) * 32 * 24 + o);
+          ap[n][0] = alpha[buf * 32 + 8 * n + 2 * tq];
+          ap[n][1] = alpha[buf * 32 + 8 * n + 2 * tq + 1];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int mt = qw + 8 * i;
+        if (mt < ktot) {
+          uint32_t ah[4], al_[4];
+          const int off = lds_at_row(lane) * fpitch + 16 * mt + lds_at_col(lane);
+          ldsm_x4_t(ah, fh + off);
+          ldsm_x4_t(al_, fl + off);
+#pragma unroll
+          for (int n = 0; n < 4; ++n) {
+            if (n < NT) {
+              Gacc[i][n][0] *= ap[n][0];
+              Gacc[i][n][1] *= ap[n][1];
+              Gacc[i][n][2] *= ap[n][0];
+              Gacc[i][n][3] *= ap[n][1];
+              mma16816<__half>(Gacc[i][n], ah, bf[n]);
+              mma16816<__half>(Gacc[i][n], al_, bf[n]);
+              mma16816<__half>(Gacc[i][n], ah, bl[n]);
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty_sp + buf);
+    WS_TICK(9);
+  }
+
+  // ---- chunk partials ---------------------------------------------------------------------------
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {
+    lsum0 += __shfl_xor_sync(0xffffffffu, lsum0, o);
+    lsum1 += __shfl_xor_sync(0xffffffffu, lsum1, o);
+  }
+  if (act && half == 1 && gq == 0) {
+    lx[nt * 8 + 2 * tq] = lsum0;
+    lx[nt * 8 + 2 * tq + 1] = lsum1;
+  }
+  __syncthreads();   // the spectral warps have zeroed this chunk's verbatim-V partial
+  if (act && half == 0 && gq == 0) {
+    if (hc0 < Hq) {
+      p.m_part[slot_id * Hq + hc0] = m_run0;
+      p.l_part[slot_id * Hq + hc0] = lsum0 + lx[nt * 8 + 2 * tq];
+    }
+    if (hc0 + 1 < Hq) {
+      p.m_part[slot_id * Hq + hc0 + 1] = m_run1;
+      p.l_part[slot_id * Hq + hc0 + 1] = lsum1 + lx[nt * 8 + 2 * tq + 1];
+    }
+  }
+  if (act) {
+    // both halves add their numerators (two addends onto zero: the order does not change the sum)
+    float* ob = p.o_part + slot_id * Hq * D;
+#pragma unroll
+    for (int i = 0; i < WS_MTV; ++i) {
+      if (i < mtvn) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int c = 16 * (mtv0 + i) + gq + 8 * (e >> 1);
+          const int h = hc0 + (e & 1);
+          if (c < Mn_v && h < Hq) {
+            const int g = h / R;
+            if (c >= a.vn_h[g] && c < a.vn_h[g + 1]) atomicAdd(ob + h * D + a.vn_list[c] - g * D, Oacc[i][e]);
+          }
+        }
+      }
+    }
+  }
+  float* gb = p.g_part + (((int64_t)b * p.n_mid_chunks + chunk) * Hq) * 2 * N;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int mt = qw + 8 * i;
+    if (mt < ktot) {
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        if (n < NT) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int row = 16 * mt + gq + 8 * (e >> 1);
+            const int h = 8 * n + 2 * tq + (e & 1);
+            if (row < 2 * N && h < Hq) gb[(int64_t)h * 2 * N + row] = Gacc[i][n][e];
+          }
+        }
+      }
+    }
+  }
+}
+
+#ifdef FA_PHASE_TIMING
+#undef WS_TICK
+#endif

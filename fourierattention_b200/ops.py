@@ -15,7 +15,7 @@ ANGLE_EXACT, ANGLE_KM57 = _lib.FA_ANGLE_EXACT, _lib.FA_ANGLE_KM57
 
 _scratch = {}
 launch_count = 0          # kernels-launching C-ABI calls made so far (for benchmark accounting)
-last_decode_path = None   # fa_decode_path() of the most recent decode_attn call (1 = tensor-core pass)
+last_decode_path = None   # fa_decode_path() of the most recent decode_attn call (0 exact, 1 tensor-core pass, 2 warp-specialised)
 
 
 def _dt(t):
@@ -169,6 +169,10 @@ class DecodeTables:
             return torch.as_tensor(t).to(device=device, dtype=torch.int32).contiguous()
         self.kc_list, self.kc_h, self.kn_list, self.kn_h = cv(kc_list), cv(kc_h), cv(kn_list), cv(kn_h)
         self.vc_list, self.vc_h, self.vn_list, self.vn_h = cv(vc_list), cv(vc_h), cv(vn_list), cv(vn_h)
+        # host copies of the two verbatim offset tables: the planner reads them to choose the kernel
+        kh, vh = self.kn_h.cpu().tolist(), self.vn_h.cpu().tolist()
+        self.kn_h_host = (C.c_int32 * len(kh))(*kh)
+        self.vn_h_host = (C.c_int32 * len(vh))(*vh)
 
 
 def decode_attn(q, k_sink, v_sink, k_win, v_win, k_mn, v_mn, k_coef, v_coef,
@@ -233,6 +237,8 @@ def decode_attn(q, k_sink, v_sink, k_win, v_win, k_mn, v_mn, k_coef, v_coef,
                                                 tb.kn_h.data_ptr())
         a.vc_list, a.vc_h, a.vn_list, a.vn_h = (tb.vc_list.data_ptr(), tb.vc_h.data_ptr(), tb.vn_list.data_ptr(),
                                                 tb.vn_h.data_ptr())
+        a.kn_h_host = C.cast(tb.kn_h_host, C.c_void_p)
+        a.vn_h_host = C.cast(tb.vn_h_host, C.c_void_p)
     if out is None:
         out = torch.empty((B, num_head_q, D), dtype=torch.float32, device=dev)
     a.out = out.data_ptr()

@@ -158,8 +158,13 @@ typedef struct {
   void* scratch;
   size_t scratch_bytes;
   /* optional profiling aid: a HOST array of five cudaEvent_t recorded on `stream` before the first
-   * launch and after each of the four launches (prepare, main, contract, output); null = off   */
+   * launch and after each launch (prepare, main; the third and fourth event both follow main, the fifth follows
+   * finish); null = off   */
   void* const* phase_events_host;
+  /* optional HOST copies of kn_h and vn_h (Hkv + 1 entries each); with them the planner can check the
+   * per-head column ranges and pick the warp-specialised middle-span pass; null = not given          */
+  const int32_t* kn_h_host;
+  const int32_t* vn_h_host;
 } fa_decode_args_t;
 
 /* Bytes of scratch fa_decode_attn needs for this geometry (only the size fields are read). */
@@ -167,8 +172,11 @@ size_t fa_decode_scratch_bytes(const fa_decode_args_t* args_host);
 /* Which middle-span pass fa_decode_attn will run for these arguments (sizes, strides and pointer
  * alignment are read): 1 = tensor-core pass (the spectral score is evaluated at 16 nodes per 64/128-token
  * super-tile and interpolated; needs N % 8 == 0, N <= 256, Hq <= 32, Mn_* <= 256, 16-byte aligned verbatim
- * rows and at most 1.5 turns of the highest frequency per super-tile), 0 = exact CUDA-core pass,
- * negative = fa_status_t.  Setting the environment variable FA_DECODE_EXACT forces 0. */
+ * rows and at most 1.5 turns of the highest frequency per super-tile), 2 = the same mathematics with the
+ * warps of a CTA specialised and pipelined (additionally needs 128-token super-tiles, kn_h_host / vn_h_host,
+ * and per 8 query heads at most 64 verbatim-K and 64 verbatim-V columns after rounding to 16), 0 = exact
+ * CUDA-core pass, negative = fa_status_t.  The environment variable FA_DECODE_EXACT forces 0,
+ * FA_DECODE_NO_WS keeps 2 from being chosen. */
 int fa_decode_path(const fa_decode_args_t* args_host);
 int fa_decode_attn(const fa_decode_args_t* args_host, fa_stream_t stream);
 
