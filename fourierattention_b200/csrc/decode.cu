@@ -37,8 +37,14 @@ struct DecodeParams {
   // 64 x 64 elements, 128-byte swizzle, out-of-range rows and columns read as zero
   alignas(64) CUtensorMap tm_k;
   alignas(64) CUtensorMap tm_v;
+  // tensor maps of the sink and window rows (tensor-core sinks+window pass): 64 columns x TRm rows
+  alignas(64) CUtensorMap tm_ks;
+  alignas(64) CUtensorMap tm_vs;
+  alignas(64) CUtensorMap tm_kw;
+  alignas(64) CUtensorMap tm_vw;
   fa_decode_args_t a;
   int R, F, n_il;
+  int TRm, il_tpc;  // tensor-core sinks+window pass: rows per tile, tiles per chunk
   float c2;  // sm_scale * log2(e)
   // plan
   int J, kvh, HG, HGp, n_groups, TR, Hqp;
@@ -700,6 +706,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) decode_main_kernel(const __gri
 
 #include "decode_fast.cuh"
 
+#include "decode_il.cuh"
 #include "decode_ws.cuh"
 
 constexpr int FAST_THREADS = FAST_T;
@@ -712,8 +719,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) decode_main_fast_kernel(const
   const long long cta_t0 = clock64();
 #endif
   if ((int)blockIdx.x < p.n_il_chunks) {
-    if (threadIdx.x >= DEC_THREADS) return;   // the sinks+window pass is written for 256 threads
-    il_chunk<T>(p, b, blockIdx.x, smem_raw);
+    il_chunk_mma<T>(p, b, blockIdx.x, smem_raw);
   } else {
     mid_chunk_fast<T, NT, NH>(p, b, blockIdx.x - p.n_il_chunks, smem_raw);
   }
@@ -731,8 +737,7 @@ __global__ void __launch_bounds__(WS_T, 1) decode_main_ws_kernel(const __grid_co
   const long long cta_t0 = clock64();
 #endif
   if ((int)blockIdx.x < p.n_il_chunks) {
-    if (threadIdx.x >= DEC_THREADS) return;   // the sinks+window pass is written for 256 threads
-    il_chunk<T>(p, b, blockIdx.x, smem_raw);
+    il_chunk_mma<T>(p, b, blockIdx.x, smem_raw);
 #ifdef FA_PHASE_TIMING
     if (threadIdx.x == 0) atomicAdd(&g_phase_clk[14], (unsigned long long)(clock64() - cta_t0));
 #endif
@@ -912,7 +917,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
   p.il_chunk_rows = p.n_il > 0 ? rup(ceil_div(p.n_il, p.n_il_chunks), TR) : TR;
   p.n_il_chunks = p.n_il > 0 ? ceil_div(p.n_il, p.il_chunk_rows) : 0;
 
-  int mid_smem_bytes = 0;
+  int mid_smem_bytes = 0, il_smem_fast = 0;
   p.J = 8; p.kvh = 1; p.HG = p.R; p.HGp = 8; p.n_groups = 1; p.pitchK = p.pitchV = 16; p.qpitch = 4;
   p.n_mid_chunks = 0; p.mid_chunk = 8;
   if (a.n_mid > 0) {
@@ -952,7 +957,13 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
     {
       const int NT = ceil_div(a.Hq, 8);
       auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-      const bool shape_ok = a.N % 8 == 0 && a.N <= 256 && NT <= FNT_MAX && a.Mn_k <= 256 && a.Mn_v <= 256;
+      // rows per tile of the tensor-core sinks+window pass: three ring stages have to fit
+      int TRm = 128;
+      while (TRm > 16 && il_mma_smem(TRm, p.F, a.Hkv, a.D, a.dtype == FA_DTYPE_BF16).total > 227 * 1024) TRm >>= 1;
+      il_smem_fast = il_mma_smem(TRm, p.F, a.Hkv, a.D, a.dtype == FA_DTYPE_BF16).total;
+      p.TRm = TRm;
+      const bool shape_ok = a.N % 8 == 0 && a.N <= 256 && NT <= FNT_MAX && a.Mn_k <= 256 && a.Mn_v <= 256 &&
+                            a.D % 16 == 0 && il_smem_fast <= 227 * 1024;
       const bool align_ok = (a.Mn_k == 0 || (al16(a.k_mn) && a.k_mn_sk % 8 == 0 && a.k_mn_sb % 8 == 0)) &&
                             (a.Mn_v == 0 || (al16(a.v_mn) && a.v_mn_sk % 8 == 0 && a.v_mn_sb % 8 == 0));
       int NH = 0;
@@ -990,25 +1001,28 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
     const int max_chunks = ceil_div(a.n_mid, J);
     if (p.fast && p.n_il > 0) {
       // One wave of CTAs per launch.  Split the CTAs of a sequence between sinks+window rows and the
-      // middle span so that the slowest CTA is as short as possible; measured costs on B200 in clock
-      // ticks: 870 per sinks+window row (CUDA cores), 24 K set-up + 142 per middle-span token.
+      // middle span so that the slowest CTA is as short as possible; costs in clock ticks as measured
+      // on B200 (cost_il_row per sinks+window row, cost_mid_tok per middle-span token, plus set-up).
       const int per_seq = sms / a.B > 2 ? sms / a.B : 2;
+      const double cost_il_row = 450.0, cost_mid_tok = p.fast == 2 ? 125.0 : 142.0;
+      const int n_tiles = ceil_div(a.n_sink, p.TRm) + ceil_div(a.n_win, p.TRm);
       double best = 1e30;
       int best_il = 1;
-      for (int n_il = 1; n_il < per_seq; ++n_il) {
-        const int il_rows = rup(ceil_div(p.n_il, n_il), TR);
-        int n_mid = per_seq - ceil_div(p.n_il, il_rows);
+      for (int n_il = 1; n_il < per_seq && n_il <= n_tiles; ++n_il) {
+        const int tpc = ceil_div(n_tiles, n_il);
+        int n_mid = per_seq - ceil_div(n_tiles, tpc);
         if (n_mid > max_chunks) n_mid = max_chunks;
         const int mid_tok = rup(ceil_div(a.n_mid, n_mid), J);
-        const double t_il = 870.0 * il_rows, t_mid = 24000.0 + 142.0 * mid_tok;
+        const double t_il = 8000.0 + cost_il_row * tpc * p.TRm, t_mid = 24000.0 + cost_mid_tok * mid_tok;
         const double t = t_il > t_mid ? t_il : t_mid;
         if (t < best) {
           best = t;
           best_il = n_il;
         }
       }
-      p.il_chunk_rows = rup(ceil_div(p.n_il, best_il), TR);
-      p.n_il_chunks = ceil_div(p.n_il, p.il_chunk_rows);
+      p.il_tpc = ceil_div(n_tiles, best_il);
+      p.n_il_chunks = ceil_div(n_tiles, p.il_tpc);
+      p.il_chunk_rows = p.il_tpc * p.TRm;
     }
     int target = ((p.fast ? 1 : 3) * sms) / (a.B * p.n_groups) - p.n_il_chunks;
     if (target < 1) target = 1;
@@ -1017,7 +1031,8 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
     p.n_mid_chunks = ceil_div(a.n_mid, p.mid_chunk);
   }
   p.NCH = p.n_il_chunks + p.n_mid_chunks;
-  p.smem_main = il_smem > mid_smem_bytes ? il_smem : mid_smem_bytes;
+  const int il_need = p.fast ? il_smem_fast : il_smem;   // the 512-thread kernels run the sinks+window rows as MMAs
+  p.smem_main = il_need > mid_smem_bytes ? il_need : mid_smem_bytes;
   if (p.n_il == 0) p.smem_main = mid_smem_bytes;
   FA_REQUIRE(p.smem_main <= 227 * 1024, FA_ERR_CAPACITY, "fa_decode_attn: shared memory need %d exceeds 227 KB", p.smem_main);
   p.smem_prepare = p.R * (a.D + 8) * 4;   // one KV head's column segment (at most D wide) plus alignment pads
@@ -1176,6 +1191,14 @@ extern "C" int fa_decode_attn(const fa_decode_args_t* args, fa_stream_t stream) 
                "fa_decode_attn: window rows must be 16-byte aligned");
   FA_REQUIRE(a.q_sb % 8 == 0 || a.B == 1, FA_ERR_ALIGN, "fa_decode_attn: q batch stride must be a multiple of 8");
   if (p.fast) {
+    if (a.n_sink > 0 &&
+        ((rc = make_tensor_map_3d(&p.tm_ks, a.k_sink, a.dtype, p.F, a.n_sink, p.F, a.B, a.sink_sb, 64, p.TRm)) != FA_OK ||
+         (rc = make_tensor_map_3d(&p.tm_vs, a.v_sink, a.dtype, p.F, a.n_sink, p.F, a.B, a.sink_sb, 64, p.TRm)) != FA_OK))
+      return rc;
+    if (a.n_win > 0 &&
+        ((rc = make_tensor_map_3d(&p.tm_kw, a.k_win, a.dtype, p.F, a.n_win, p.F, a.B, a.win_sb, 64, p.TRm)) != FA_OK ||
+         (rc = make_tensor_map_3d(&p.tm_vw, a.v_win, a.dtype, p.F, a.n_win, p.F, a.B, a.win_sb, 64, p.TRm)) != FA_OK))
+      return rc;
     if (a.Mn_k > 0 && (rc = make_tensor_map_3d(&p.tm_k, a.k_mn, a.dtype, a.Mn_k, a.n_mid, a.k_mn_sk, a.B, a.k_mn_sb, 64, 64)) != FA_OK)
       return rc;
     if (a.Mn_v > 0 && (rc = make_tensor_map_3d(&p.tm_v, a.v_mn, a.dtype, a.Mn_v, a.n_mid, a.v_mn_sk, a.B, a.v_mn_sb, 64, 64)) != FA_OK)

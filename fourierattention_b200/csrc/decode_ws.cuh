@@ -275,9 +275,11 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
       WS_TICK(11);
       // ---- scores at the nodes: s_node[16 x HN] = Fn_t[16 x 2N] * w[2N x HN] -----------------------
       if (nt1 < NT) {
-        float acc[4][4];
+        // consecutive MMAs never share an accumulator: a dependent MMA would wait out the whole latency
+        // of the one before it
+        float acc[6][4];
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 6; ++c)
 #pragma unroll
           for (int e = 0; e < 4; ++e) acc[c][e] = 0.f;
 #pragma unroll
@@ -288,17 +290,18 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
             const int off = lds_a_row(lane) * fpitch + 16 * ks + lds_a_col(lane);
             ldsm_x4(ah, fh + off);
             ldsm_x4(al, fl + off);
-            mma16816<__half>(acc[i & 3], ah, bhi[i]);
-            mma16816<__half>(acc[i & 3], al, bhi[i]);
-            mma16816<__half>(acc[i & 3], ah, blo[i]);
+            mma16816<__half>(acc[3 * (i & 1)], ah, bhi[i]);
+            mma16816<__half>(acc[3 * (i & 1) + 1], al, bhi[i]);
+            mma16816<__half>(acc[3 * (i & 1) + 2], ah, blo[i]);
           }
         }
         float* red = snode32 + khalf * (FD * HN);
         const int col = 8 * nt1 + 2 * tq;
-        red[gq * HN + col] = (acc[0][0] + acc[1][0]) + (acc[2][0] + acc[3][0]);
-        red[gq * HN + col + 1] = (acc[0][1] + acc[1][1]) + (acc[2][1] + acc[3][1]);
-        red[(gq + 8) * HN + col] = (acc[0][2] + acc[1][2]) + (acc[2][2] + acc[3][2]);
-        red[(gq + 8) * HN + col + 1] = (acc[0][3] + acc[1][3]) + (acc[2][3] + acc[3][3]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float v = ((acc[0][e] + acc[3][e]) + (acc[1][e] + acc[4][e])) + (acc[2][e] + acc[5][e]);
+          red[(gq + 8 * (e >> 1)) * HN + col + (e & 1)] = v;
+        }
       }
       ws_group_sync(1);
       WS_TICK(12);
@@ -324,7 +327,11 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
   // ============================= score warps ======================================================
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(WS_QREG));
 #ifdef FA_PHASE_TIMING
+#ifdef FA_IL_TIMING
+  const bool ticker__ = false;
+#else
   const bool ticker__ = (tid == 256);
+#endif
   long long tick__ = clock64();
 #endif
   const int qw = wp - 8, nt = qw & 3, half = qw >> 2;
@@ -340,6 +347,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
     mtv0 = a.vn_h[g0] >> 4;
     mtvn = ((a.vn_h[g1 + 1] + 15) >> 4) - mtv0;
   }
+  const int nks = (kc1 - kc0) >> 4;   // 16-column steps of the verbatim-K contraction
   // the heads' verbatim-K query entries as MMA B fragments (raw model-dtype values; the softmax
   // scale is applied to the fp32 sums)
   uint32_t bq[WS_KS][2];
@@ -387,8 +395,6 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
     const int tok0 = l0 + st * J + half * FH;   // first token of this warp's half
     const __half* fh = fnt + (buf * 2 + 0) * FD * fpitch;
     const __half* fl = fnt + (buf * 2 + 1) * FD * fpitch;
-    mbar_wait(full_sp + buf, (st >> 1) & 1, dead, p.err);
-    WS_TICK(0);
     float sc[4][4];
 #pragma unroll
     for (int mt = 0; mt < 4; ++mt)
@@ -396,43 +402,30 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
       for (int e = 0; e < 4; ++e) sc[mt][e] = 0.f;
     const int iK = 4 * st + half, sK = iK % 3;
     const uint32_t parK = (uint32_t)(iK / 3) & 1u;
+    // Every run of MMAs below visits four different accumulators in turn: a dependent MMA issued right
+    // after its predecessor would wait out that one's whole latency.
     if (act) {
-      // ---- interpolate the node scores to this warp's 64 tokens ---------------------------------
-      uint32_t bh[2], bl[2];
-      const int boff = (8 * nt + lds_b_row(lane)) * 24 + lds_b_col(lane);
-      ldsm_x2(bh, snode + (buf * 2 + 0) * 32 * 24 + boff);
-      ldsm_x2(bl, snode + (buf * 2 + 1) * 32 * 24 + boff);
-#pragma unroll
-      for (int mt = 0; mt < 4; ++mt) {
-        uint32_t ah[4], al[4];
-        const int off = (half * FH + 16 * mt + lds_a_row(lane)) * 24 + lds_a_col(lane);
-        ldsm_x4(ah, interp_hi + off);
-        ldsm_x4(al, interp_lo + off);
-        mma16816<__half>(sc[mt], ah, bh);
-        mma16816<__half>(sc[mt], al, bh);
-        mma16816<__half>(sc[mt], ah, bl);
-      }
-      WS_TICK(1);
-      // ---- verbatim-dim scores from the K rows ---------------------------------------------------
+      // ---- verbatim-dim scores from the K rows (needs only the K tile, so it comes first) -----------
       mbar_wait(full_slot + sK, parK, dead, p.err);
       WS_TICK(2);
       const unsigned char* ks_ = slots + sK * L.slot_bytes;
 #pragma unroll
-      for (int mt = 0; mt < 4; ++mt) {
-        float vb[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int ks = 0; ks < WS_KS; ++ks) {
+        if (ks < nks) {
 #pragma unroll
-        for (int ks = 0; ks < WS_KS; ++ks) {
-          const int c = kc0 + 16 * ks;
-          if (c < kc1) {
+          for (int mt = 0; mt < 4; ++mt) {
             uint32_t af[4];
-            ldsm_x4(af, ks_ + sw_off(16 * mt + lds_a_row(lane), (c + lds_a_col(lane)) >> 3));
-            mma16816<T>(vb, af, bq[ks]);
+            ldsm_x4(af, ks_ + sw_off(16 * mt + lds_a_row(lane), (kc0 + 16 * ks + lds_a_col(lane)) >> 3));
+            mma16816<T>(sc[mt], af, bq[ks]);
           }
         }
-        sc[mt][0] += p.c2 * vb[0] + cst0;
-        sc[mt][1] += p.c2 * vb[1] + cst1;
-        sc[mt][2] += p.c2 * vb[2] + cst0;
-        sc[mt][3] += p.c2 * vb[3] + cst1;
+      }
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        sc[mt][0] = p.c2 * sc[mt][0] + cst0;
+        sc[mt][1] = p.c2 * sc[mt][1] + cst1;
+        sc[mt][2] = p.c2 * sc[mt][2] + cst0;
+        sc[mt][3] = p.c2 * sc[mt][3] + cst1;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_slot + sK);
@@ -444,6 +437,35 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
       issue_tile(iK + 3);
       WS_TICK(11);
     }
+    mbar_wait(full_sp + buf, (st >> 1) & 1, dead, p.err);
+    WS_TICK(0);
+    if (act) {
+      // ---- add the node scores interpolated to this warp's 64 tokens ---------------------------------
+      uint32_t bh[2], bl[2];
+      const int boff = (8 * nt + lds_b_row(lane)) * 24 + lds_b_col(lane);
+      ldsm_x2(bh, snode + (buf * 2 + 0) * 32 * 24 + boff);
+      ldsm_x2(bl, snode + (buf * 2 + 1) * 32 * 24 + boff);
+      const int ioff = (half * FH + lds_a_row(lane)) * 24 + lds_a_col(lane);
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        uint32_t al[4];
+        ldsm_x4(al, interp_lo + ioff + 16 * mt * 24);
+        mma16816<__half>(sc[mt], al, bh);
+      }
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        uint32_t ah[4];
+        ldsm_x4(ah, interp_hi + ioff + 16 * mt * 24);
+        mma16816<__half>(sc[mt], ah, bl);
+      }
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        uint32_t ah[4];
+        ldsm_x4(ah, interp_hi + ioff + 16 * mt * 24);
+        mma16816<__half>(sc[mt], ah, bh);
+      }
+    }
+    WS_TICK(1);
     // ---- softmax over the 128 tokens of the super-tile (both halves agree on the maximum) ----------
     float al0 = 1.f, al1 = 1.f;
     float pf[4][4];   // probabilities, already rounded to fp16
@@ -504,18 +526,27 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) ldsm_x2(bp[ks], pw16 + lds_b_row(lane) * 72 + 16 * ks + lds_b_col(lane));
       {
-        float pt2[4] = {0.f, 0.f, 0.f, 0.f};
+        float pt2[3][4];
+#pragma unroll
+        for (int c = 0; c < 3; ++c)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) pt2[c][e] = 0.f;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
           uint32_t af[4], al_[4];
           const int ioff = (half * FH + 16 * ks + lds_at_row(lane)) * 24 + lds_at_col(lane);
           ldsm_x4_t(af, interp_hi + ioff);
           ldsm_x4_t(al_, interp_lo + ioff);
-          mma16816<__half>(pt_acc, af, bp[ks]);
-          mma16816<__half>(pt2, al_, bp[ks]);
+          if (ks & 1) {
+            mma16816<__half>(pt2[0], af, bp[ks]);
+            mma16816<__half>(pt2[1], al_, bp[ks]);
+          } else {
+            mma16816<__half>(pt_acc, af, bp[ks]);
+            mma16816<__half>(pt2[2], al_, bp[ks]);
+          }
         }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) pt_acc[e] += pt2[e];
+        for (int e = 0; e < 4; ++e) pt_acc[e] = (pt_acc[e] + pt2[0][e]) + (pt2[1][e] + pt2[2][e]);
       }
       WS_TICK(5);
       // ---- verbatim-V numerators -------------------------------------------------------------------
@@ -553,14 +584,21 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
         Oacc[i][1] *= al1;
         Oacc[i][2] *= al0;
         Oacc[i][3] *= al1;
-        if (i < mtvn) {
+      }
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            uint32_t af[4];
-            ldsm_x4_t(af, vs_ + sw_off(16 * ks + lds_at_row(lane), (16 * (mtv0 + i) + lds_at_col(lane)) >> 3));
-            mma16816<T>(Oacc[i], af, bp[ks]);
-            if (kBf16) mma16816<T>(Oacc[i], af, bp_lo[ks]);
-          }
+      for (int ks = 0; ks < 4; ++ks) {
+        uint32_t af[WS_MTV][4];
+#pragma unroll
+        for (int i = 0; i < WS_MTV; ++i)
+          if (i < mtvn)
+            ldsm_x4_t(af[i], vs_ + sw_off(16 * ks + lds_at_row(lane), (16 * (mtv0 + i) + lds_at_col(lane)) >> 3));
+#pragma unroll
+        for (int i = 0; i < WS_MTV; ++i)
+          if (i < mtvn) mma16816<T>(Oacc[i], af[i], bp[ks]);
+        if (kBf16) {
+#pragma unroll
+          for (int i = 0; i < WS_MTV; ++i)
+            if (i < mtvn) mma16816<T>(Oacc[i], af[i], bp_lo[ks]);
         }
       }
       __syncwarp();
@@ -629,11 +667,17 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
               Gacc[i][n][1] *= ap[n][1];
               Gacc[i][n][2] *= ap[n][0];
               Gacc[i][n][3] *= ap[n][1];
-              mma16816<__half>(Gacc[i][n], ah, bf[n]);
-              mma16816<__half>(Gacc[i][n], al_, bf[n]);
-              mma16816<__half>(Gacc[i][n], ah, bl[n]);
             }
           }
+#pragma unroll
+          for (int n = 0; n < 4; ++n)
+            if (n < NT) mma16816<__half>(Gacc[i][n], al_, bf[n]);
+#pragma unroll
+          for (int n = 0; n < 4; ++n)
+            if (n < NT) mma16816<__half>(Gacc[i][n], ah, bl[n]);
+#pragma unroll
+          for (int n = 0; n < 4; ++n)
+            if (n < NT) mma16816<__half>(Gacc[i][n], ah, bf[n]);
         }
       }
     }
