@@ -29,7 +29,9 @@
 constexpr int WS_MTV = 4;   // 16-column tiles of verbatim V a score warp owns
 constexpr int WS_KS = 4;    // 16-column steps of verbatim K a score warp contracts
 constexpr int WS_T = 512;
-constexpr int WS_SREG = 104, WS_QREG = 152;   // registers per thread of the two groups (sum = 2 x 128)
+constexpr int WS_SREG = 56, WS_QREG = 200;   // registers per thread of the two groups (sum = 2 x 128): the
+// score warps must not spill (with 222 KB of shared memory the L1 that would catch spills is tiny), the spectral
+// warps have time to spare
 
 #ifdef FA_PHASE_TIMING
 #define WS_TICK(i)                                                      \
@@ -243,7 +245,11 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
       if (j >= 2) mbar_wait(empty_sp + buf, ((j >> 1) - 1) & 1, dead, p.err);
       WS_TICK(10);
       // ---- node basis: rotate the table to this super-tile's centre ------------------------------
+#ifdef WS_EXPERIMENT_NO_S
+      if (false) {
+#else
       if (2 * np < N) {
+#endif
         float rc[2], rs[2];
 #pragma unroll
         for (int f = 0; f < 2; ++f) {
@@ -274,7 +280,11 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
       ws_group_sync(1);
       WS_TICK(11);
       // ---- scores at the nodes: s_node[16 x HN] = Fn_t[16 x 2N] * w[2N x HN] -----------------------
+#ifdef WS_EXPERIMENT_NO_S
+      if (false) {
+#else
       if (nt1 < NT) {
+#endif
         // consecutive MMAs never share an accumulator: a dependent MMA would wait out the whole latency
         // of the one before it
         float acc[6][4];
