@@ -327,15 +327,15 @@ def ours_arm(args, w):
         op_bytes, main_bytes = algorithmic_bytes(w, n_mid, frac_heads)
         achieved = main_bytes * B / (main_avg * 1e-3) / 1e9
         step_bytes = op_bytes * B * L
-        # DRAM read+write bytes of one launch from the committed ncu capture of `profile_small`, whose launches
-        # have this workload's per-launch shape: 303.7 MB measured against 294.1 MB algorithmic.
+        # DRAM read+write bytes of one launch from the committed ncu captures of `profile_small`, whose
+        # launches have this workload's per-launch shape (algorithmic bytes 294.1 MB)
         fast = ops.last_decode_path in (1, 2)
         kernel_name = {0: "decode_main_kernel", 1: "decode_main_fast_kernel", 2: "decode_main_ws_kernel"}[ops.last_decode_path]
         traffic, traffic_src = None, None
         if fast and world == 1 and args.workload in ("llama31_8b_32k", "profile_small"):
-            traffic = 303.7e6
+            traffic = 307.3e6 if ops.last_decode_path == 2 else 303.7e6
             traffic_src = "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch of profile_small " \
-                          "(profiles/decode_main_fast_kernel.profile_small.md)"
+                          f"(profiles/{kernel_name}.profile_small.md)"
         h2d = L * B * (hq_l * D + 2 * hk * D) * 2
         d2h = L * B * hq_l * D * 4
         line = {

@@ -16,8 +16,9 @@
 // Hand-offs are mbarriers with bounded waits (node scores + basis: full/empty per buffer; K/V half
 // tiles: full/empty per ring slot); the two halves of a column tile agree on the running maximum
 // through a 64-thread named barrier, and the score warps meet once per super-tile before the g update.
-// The score warps refill the ring themselves: the nt = 0 warp of a half waits until the other warps
-// of that half have released the slot and issues the TMA boxes of the tile three places ahead.
+// The score warps refill the ring themselves: one warp of a half (column tile 0 for K tiles, tile 1 for V
+// tiles) waits until the other warps of that half have released the slot and issues the TMA boxes of the
+// tile three places ahead.
 // Registers move with the work: the spectral warps give up registers (setmaxnreg) that the score
 // warps, which hold the g and verbatim-V accumulators, take over.
 //
@@ -190,7 +191,11 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
     // =========================== spectral warps ================================================
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(WS_SREG));
 #ifdef FA_PHASE_TIMING
+#ifdef FA_TICK_S
+    const bool ticker__ = (tid == 0);
+#else
     const bool ticker__ = false;
+#endif
     long long tick__ = clock64();
 #endif
     const int nt1 = wp & 3, khalf = wp >> 2;
@@ -337,7 +342,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
   // ============================= score warps ======================================================
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(WS_QREG));
 #ifdef FA_PHASE_TIMING
-#ifdef FA_IL_TIMING
+#if defined(FA_IL_TIMING) || defined(FA_TICK_S)
   const bool ticker__ = false;
 #else
   const bool ticker__ = (tid == 256);
@@ -346,6 +351,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
 #endif
   const int qw = wp - 8, nt = qw & 3, half = qw >> 2;
   const bool act = nt < NT;
+  const int v_issuer = NT > 1 ? 1 : 0;   // column tile whose warp refills V slots (tile 0's warp refills K slots)
   __half* pw16 = reinterpret_cast<__half*>(smem + L.pw) + qw * 8 * 72;   // this warp's probabilities
   T* pwT = reinterpret_cast<T*>(pw16);
   // column ranges of this warp's heads in the verbatim stores
@@ -615,7 +621,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
       if (lane == 0) mbar_arrive(empty_slot + sV);
     }
     WS_TICK(7);
-    if (nt == 0) {
+    if (nt == v_issuer) {
       mbar_wait(empty_slot + sV, parV, dead, p.err);
       WS_TICK(12);
       issue_tile(iV + 3);

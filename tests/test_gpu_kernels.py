@@ -84,6 +84,36 @@ def test_decode_attn_tensor_core_pass(name, monkeypatch):
     assert np.abs(host(exact) - ideal).max() <= 3e-5 * max(1.0, np.abs(ideal).max())
 
 
+def _state_ramp(g):
+    """Like _state, but the keys grow along the sequence, so the running maxima of the softmax keep
+    rising from tile to tile and every accumulator is rescaled again and again."""
+    tables, k, v, qs = case_inputs(g)
+    P = g["P"]
+    ramp = (0.2 + 2.8 * np.arange(k.shape[2]) / P).astype(np.float32)
+    k = fo.rnd(k.astype(np.float32) * ramp[None, None, :, None], g["dtype"])
+    oc = oracle_cache(g, tables)
+    oc.update(k[:, :, :P], v[:, :, :P], 0)
+    oc.update(k[:, :, P:P + 1], v[:, :, P:P + 1], 0)
+    return oc, qs[0]
+
+
+@pytest.mark.parametrize("name", ["fast_32heads_fp16", "fast_gqa4_bf16", "fast_gqa3_half_tiles"])
+def test_decode_attn_rising_scores(name, monkeypatch):
+    import fourierattention_b200.ops as ops
+    g = FAST_CASES[name]
+    oc, q = _state_ramp(g)
+    inp = decode_inputs_from_oracle(oc, g["dtype"])
+    qd = dev(q, g["dtype"])
+    ideal = oc.attend(q, 0, g["Hq"], g["Hkv"], faithful=False)[:, :, 0]
+    for env in (None, "FA_DECODE_NO_WS"):
+        if env:
+            monkeypatch.setenv(env, "1")
+        out = ops.decode_attn(qd, num_head_q=g["Hq"], num_head_kv=g["Hkv"], T=oc.T, **inp)
+        assert ops.last_decode_path in (1, 2)
+        err = np.abs(host(out) - ideal).max()
+        assert err <= 1.5e-4 * max(1.0, np.abs(ideal).max()), (env, err)
+
+
 def _state(g):
     tables, k, v, qs = case_inputs(g)
     oc = oracle_cache(g, tables)
