@@ -4,6 +4,8 @@
 // All phases are formed as (position * frequency) mod period in integers, so the basis keeps full
 // float32 accuracy at any context length.  Accumulation is float32 over bounded chunks of the
 // token axis; chunk partials are reduced in a fixed order.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace fa {
@@ -340,6 +342,8 @@ __global__ void recon_finalize_kernel(const float* __restrict__ part, int nchunk
   dev[(int64_t)b * Mc + col] = fmaxf(mx - a, a - mn);
 }
 
+#include "recon_interp.cuh"
+
 // stand-alone inverse; one thread per output element (an API-completeness path, not a hot one)
 __global__ void fourier_inverse_kernel(const float* __restrict__ c, int N, int K, uint32_t T, float* __restrict__ out) {
   const int m = blockIdx.y;
@@ -440,10 +444,22 @@ extern "C" int fa_evict_update(float* k_coef, const void* k_row, int64_t k_row_s
   return FA_OK;
 }
 
+// chunks of super-tiles per (column tile, sequence) of the interpolating kernel; depends on the sizes only,
+// so that the scratch query does not need N and T
+static int recon_interp_chunks(int B, int K, int Mc) {
+  const int64_t tiles = (int64_t)ceil_div(Mc, RI_CT) * B;
+  int want = (int)ceil_div64(2 * 148, tiles);
+  const int maxc = ceil_div(K, 128);
+  if (want < 1) want = 1;
+  if (want > maxc) want = maxc;
+  return want;
+}
+
 extern "C" size_t fa_recon_stats_scratch_bytes(int B, int K, int Mc) {
   if (B <= 0 || K <= 0 || Mc <= 0) return 0;
   ReconPlan p = recon_plan(B, K, Mc);
-  return (size_t)B * p.nchunk * 3 * Mc * sizeof(float);
+  const int nc = recon_interp_chunks(B, K, Mc);
+  return (size_t)B * (p.nchunk > nc ? p.nchunk : nc) * 3 * Mc * sizeof(float);
 }
 
 extern "C" int fa_recon_stats(const float* coef, int B, int N, int Mc, int K, int T, float* avg, float* dev,
@@ -456,11 +472,34 @@ extern "C" int fa_recon_stats(const float* coef, int B, int N, int Mc, int K, in
   FA_REQUIRE(scratch_bytes >= need, FA_ERR_CAPACITY, "fa_recon_stats: scratch too small (%zu < %zu bytes)",
              scratch_bytes, need);
   cudaStream_t st = (cudaStream_t)stream;
-  dim3 grid(p.m_tiles, p.nchunk, B);
-  recon_stats_kernel<<<grid, 256, 0, st>>>(coef, N, Mc, K, (uint32_t)T, (float*)scratch, p.kchunk, p.nchunk);
+  // interpolating kernel: needs at most 1.5 turns of the highest frequency per 128- or 64-token super-tile
+  int J = 0;
+  if ((int64_t)128 * (N - 1) * 2 <= (int64_t)3 * T) J = 128;
+  else if ((int64_t)64 * (N - 1) * 2 <= (int64_t)3 * T) J = 64;
+  int nchunk = p.nchunk;
+  if (J > 0 && N <= 256 && getenv("FA_RECON_DIRECT") == nullptr) {
+    nchunk = recon_interp_chunks(B, K, Mc);
+    const int nst = ceil_div(K, J);
+    const int spc = ceil_div(nst, nchunk);
+    nchunk = ceil_div(nst, spc);
+    const int smem = ri_smem(N, J).total;
+    dim3 grid(ceil_div(Mc, RI_CT), nchunk, B);
+    if (J == 128) {
+      cudaError_t e = cudaFuncSetAttribute(recon_stats_interp_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
+      recon_stats_interp_kernel<128><<<grid, RI_T, smem, st>>>(coef, N, Mc, K, (uint32_t)T, (float*)scratch, spc, nchunk);
+    } else {
+      cudaError_t e = cudaFuncSetAttribute(recon_stats_interp_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
+      recon_stats_interp_kernel<64><<<grid, RI_T, smem, st>>>(coef, N, Mc, K, (uint32_t)T, (float*)scratch, spc, nchunk);
+    }
+  } else {
+    dim3 grid(p.m_tiles, p.nchunk, B);
+    recon_stats_kernel<<<grid, 256, 0, st>>>(coef, N, Mc, K, (uint32_t)T, (float*)scratch, p.kchunk, p.nchunk);
+  }
   FA_CHECK_LAUNCH("fa_recon_stats");
   dim3 g2(ceil_div(Mc, 128), B);
-  recon_finalize_kernel<<<g2, 128, 0, st>>>((const float*)scratch, p.nchunk, Mc, K, avg, dev);
+  recon_finalize_kernel<<<g2, 128, 0, st>>>((const float*)scratch, nchunk, Mc, K, avg, dev);
   FA_CHECK_LAUNCH("fa_recon_stats(finalize)");
   return FA_OK;
 }

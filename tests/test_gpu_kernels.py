@@ -287,7 +287,8 @@ def test_colstats_and_gather(dtype):
     assert float(out[:, 0].abs().sum()) == 0 and float(out[:, :, 37:].abs().sum()) == 0
 
 
-@pytest.mark.parametrize("B,N,Mc,K,T", [(1, 4, 9, 30, 35), (2, 16, 70, 500, 777), (1, 128, 130, 3000, 3333)])
+@pytest.mark.parametrize("B,N,Mc,K,T", [(1, 4, 9, 30, 35), (2, 16, 70, 500, 777), (1, 128, 130, 3000, 3333),
+                                          (2, 32, 100, 5000, 9000), (1, 256, 40, 9001, 40000)])
 def test_recon_stats_matches_oracle(B, N, Mc, K, T):
     import fourierattention_b200.ops as ops
     rng = np.random.default_rng(N)
