@@ -18,7 +18,7 @@ STATUS_NAMES = {0: "FA_OK", -1: "FA_ERR_NULL", -2: "FA_ERR_SHAPE", -3: "FA_ERR_D
 # every symbol include/fourier_b200.h declares
 EXPORTS = ["fa_version", "fa_last_error_string", "fa_gather_cols", "fa_colstats", "fa_compress_scratch_bytes",
            "fa_compress", "fa_evict_update", "fa_recon_stats_scratch_bytes", "fa_recon_stats", "fa_fourier_inverse",
-           "fa_cache_step", "fa_decode_scratch_bytes", "fa_decode_path", "fa_decode_attn", "fa_decode_attn_static", "fa_merge"]
+           "fa_cache_step", "fa_evict_step", "fa_decode_scratch_bytes", "fa_decode_path", "fa_decode_attn", "fa_decode_attn_static", "fa_merge"]
 
 i32, i64, vp, f32, sz = C.c_int32, C.c_int64, C.c_void_p, C.c_float, C.c_size_t
 
@@ -71,6 +71,9 @@ def _load():
     lib.fa_recon_stats.argtypes = [vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp, vp, sz, vp]
     lib.fa_fourier_inverse.argtypes = [vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp]
     lib.fa_cache_step.argtypes = [vp, vp, i64, vp, C.c_int, vp, C.c_int, vp, i64, vp, i64, vp, vp, i64, i64, vp, vp,
+                                  i64, C.c_int, C.c_int, C.c_int, C.c_int, vp]
+    lib.fa_evict_step.argtypes = [vp, vp, i64, vp, C.c_int, vp, vp, i64, vp, C.c_int, C.c_int, i64, C.c_int, C.c_int,
+                                  vp, vp, i64, vp, C.c_int, vp, C.c_int, vp, i64, vp, i64, vp, vp, i64, i64, vp, vp,
                                   i64, C.c_int, C.c_int, C.c_int, C.c_int, vp]
     lib.fa_decode_scratch_bytes.argtypes = [C.POINTER(DecodeArgs)]
     lib.fa_decode_scratch_bytes.restype = sz

@@ -348,8 +348,6 @@ class DynamicCache(Cache):
         phase = self.curr_tokennum[layer_idx]
         row = S + st.off
         k_ev, v_ev = st.kbuf[:, row], st.vbuf[:, row]
-        ops.evict_update(st.k_coef if tb.kc_list.numel() else None, k_ev, tb.kc_list,
-                         st.v_coef if tb.vc_list.numel() else None, v_ev, tb.vc_list, phase, T_c, self.update_angle)
         appends = self.seq_shard is None or self.seq_shard[0] == self.seq_shard[1] - 1
         if appends and st.n_mid + 1 > st.k_unc.shape[1]:
             grow = lambda b: torch.cat([b, torch.empty_like(b)], dim=1)
@@ -360,7 +358,10 @@ class DynamicCache(Cache):
         else:                                                    # another rank stores the evicted row
             k_unc_row, v_unc_row = st.k_unc[:, 0], st.v_unc[:, 0]
             kn = vn = tb.kn_list[:0]
-        ops.cache_step(k_ev, v_ev, kn, vn, k_unc_row, v_unc_row, key_states, value_states,
+        # eviction into the coefficients, verbatim append and window slide in one launch
+        ops.evict_step(st.k_coef if tb.kc_list.numel() else None, tb.kc_list,
+                       st.v_coef if tb.vc_list.numel() else None, tb.vc_list, phase, T_c, self.update_angle,
+                       k_ev, v_ev, kn, vn, k_unc_row, v_unc_row, key_states, value_states,
                        st.kbuf[:, row + W], st.vbuf[:, row + W])
         if appends:
             st.n_mid += 1

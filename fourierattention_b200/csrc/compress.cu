@@ -162,12 +162,46 @@ __global__ void compress_reduce_kernel(const float* __restrict__ part, int nspli
 // =====================================================================================
 constexpr int EV_ROWS = 4;
 
+// the window slide / verbatim append of one decode step (what cache_step_kernel does), carried along by
+// the eviction kernel's third grid slice when the two are launched together
+struct StepArgs {
+  const void *k_evict, *v_evict, *k_new, *v_new;
+  const int32_t *kn_idx, *vn_idx;
+  void *k_unc, *v_unc, *k_dst, *v_dst;
+  int64_t evict_sb, k_unc_sb, v_unc_sb, new_sb, new_sh, dst_sb;
+  int Mn_k, Mn_v, Hkv, D;
+};
+
+template <typename T>
+__device__ void cache_step_body(const StepArgs& s, int b, int t0, int nthreads) {
+  const T* k_evict = reinterpret_cast<const T*>(s.k_evict);
+  const T* v_evict = reinterpret_cast<const T*>(s.v_evict);
+  T* k_unc = reinterpret_cast<T*>(s.k_unc);
+  T* v_unc = reinterpret_cast<T*>(s.v_unc);
+  for (int i = t0; i < s.Mn_k; i += nthreads) k_unc[(int64_t)b * s.k_unc_sb + i] = k_evict[(int64_t)b * s.evict_sb + s.kn_idx[i]];
+  for (int i = t0; i < s.Mn_v; i += nthreads) v_unc[(int64_t)b * s.v_unc_sb + i] = v_evict[(int64_t)b * s.evict_sb + s.vn_idx[i]];
+  const T* k_new = reinterpret_cast<const T*>(s.k_new);
+  const T* v_new = reinterpret_cast<const T*>(s.v_new);
+  T* k_dst = reinterpret_cast<T*>(s.k_dst);
+  T* v_dst = reinterpret_cast<T*>(s.v_dst);
+  const int F = s.Hkv * s.D;
+  for (int f = t0; f < F; f += nthreads) {
+    const int h = f / s.D, d = f - h * s.D;
+    k_dst[(int64_t)b * s.dst_sb + f] = k_new[(int64_t)b * s.new_sb + (int64_t)h * s.new_sh + d];
+    v_dst[(int64_t)b * s.dst_sb + f] = v_new[(int64_t)b * s.new_sb + (int64_t)h * s.new_sh + d];
+  }
+}
+
 template <typename T>
 __global__ void evict_update_kernel(float* __restrict__ k_coef, const T* __restrict__ k_row, int64_t k_row_sb,
                                     const int32_t* __restrict__ k_idx, int Mc_k, float* __restrict__ v_coef,
                                     const T* __restrict__ v_row, int64_t v_row_sb, const int32_t* __restrict__ v_idx,
-                                    int Mc_v, int N, uint64_t phase, uint32_t T_c, int angle_mode) {
+                                    int Mc_v, int N, uint64_t phase, uint32_t T_c, int angle_mode, StepArgs step) {
   const int side = blockIdx.z, b = blockIdx.y;
+  if (side == 2) {   // only launched together with a cache step: the CTAs of this slice share its work
+    cache_step_body<T>(step, b, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x);
+    return;
+  }
   float* coef = side ? v_coef : k_coef;
   if (coef == nullptr) return;
   const T* row = (side ? v_row + (int64_t)b * v_row_sb : k_row + (int64_t)b * k_row_sb);
@@ -432,15 +466,53 @@ extern "C" int fa_evict_update(float* k_coef, const void* k_row, int64_t k_row_s
   if (!k_coef && !v_coef) return FA_OK;
   dim3 grid(ceil_div(N, EV_ROWS), B, 2);
   cudaStream_t st = (cudaStream_t)stream;
+  const StepArgs none = {};
   if (dtype == FA_DTYPE_F16)
     evict_update_kernel<__half><<<grid, 256, 0, st>>>(k_coef, (const __half*)k_row, k_row_sb, k_idx, Mc_k, v_coef,
                                                       (const __half*)v_row, v_row_sb, v_idx, Mc_v, N,
-                                                      (uint64_t)phase, (uint32_t)T_c, angle_mode);
+                                                      (uint64_t)phase, (uint32_t)T_c, angle_mode, none);
   else
     evict_update_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
         k_coef, (const __nv_bfloat16*)k_row, k_row_sb, k_idx, Mc_k, v_coef, (const __nv_bfloat16*)v_row, v_row_sb,
-        v_idx, Mc_v, N, (uint64_t)phase, (uint32_t)T_c, angle_mode);
+        v_idx, Mc_v, N, (uint64_t)phase, (uint32_t)T_c, angle_mode, none);
   FA_CHECK_LAUNCH("fa_evict_update");
+  return FA_OK;
+}
+
+extern "C" int fa_evict_step(float* k_coef, const void* k_row, int64_t k_row_sb, const int32_t* k_idx, int Mc_k,
+                             float* v_coef, const void* v_row, int64_t v_row_sb, const int32_t* v_idx, int Mc_v, int N,
+                             int64_t phase, int T_c, int angle_mode, const void* k_evict, const void* v_evict,
+                             int64_t evict_sb, const int32_t* kn_idx, int Mn_k, const int32_t* vn_idx, int Mn_v,
+                             void* k_unc, int64_t k_unc_sb, void* v_unc, int64_t v_unc_sb, const void* k_new,
+                             const void* v_new, int64_t new_sb, int64_t new_sh, void* k_dst, void* v_dst,
+                             int64_t dst_sb, int dtype, int B, int Hkv, int D, fa_stream_t stream) {
+  FA_REQUIRE(dtype == FA_DTYPE_F16 || dtype == FA_DTYPE_BF16, FA_ERR_DTYPE, "fa_evict_step: bad dtype %d", dtype);
+  FA_REQUIRE(B > 0 && N > 0 && T_c > 0 && phase >= 0 && Hkv > 0 && D > 0 && Mn_k >= 0 && Mn_v >= 0, FA_ERR_SHAPE,
+             "fa_evict_step: bad sizes");
+  FA_REQUIRE(angle_mode == FA_ANGLE_EXACT || angle_mode == FA_ANGLE_KM57, FA_ERR_SHAPE,
+             "fa_evict_step: bad angle mode %d", angle_mode);
+  FA_REQUIRE(!k_coef || (k_row && Mc_k > 0), FA_ERR_NULL, "fa_evict_step: K side incomplete");
+  FA_REQUIRE(!v_coef || (v_row && Mc_v > 0), FA_ERR_NULL, "fa_evict_step: V side incomplete");
+  FA_REQUIRE(k_evict && v_evict && k_new && v_new && k_dst && v_dst, FA_ERR_NULL, "fa_evict_step: null row pointer");
+  FA_REQUIRE((Mn_k == 0 || (kn_idx && k_unc)) && (Mn_v == 0 || (vn_idx && v_unc)), FA_ERR_NULL,
+             "fa_evict_step: null verbatim store or index list");
+  StepArgs sa;
+  sa.k_evict = k_evict; sa.v_evict = v_evict; sa.k_new = k_new; sa.v_new = v_new;
+  sa.kn_idx = kn_idx; sa.vn_idx = vn_idx;
+  sa.k_unc = k_unc; sa.v_unc = v_unc; sa.k_dst = k_dst; sa.v_dst = v_dst;
+  sa.evict_sb = evict_sb; sa.k_unc_sb = k_unc_sb; sa.v_unc_sb = v_unc_sb; sa.new_sb = new_sb; sa.new_sh = new_sh;
+  sa.dst_sb = dst_sb; sa.Mn_k = Mn_k; sa.Mn_v = Mn_v; sa.Hkv = Hkv; sa.D = D;
+  dim3 grid(ceil_div(N, EV_ROWS), B, 3);   // slices 0 / 1: K / V coefficients, slice 2: the cache step
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == FA_DTYPE_F16)
+    evict_update_kernel<__half><<<grid, 256, 0, st>>>(k_coef, (const __half*)k_row, k_row_sb, k_idx, Mc_k, v_coef,
+                                                      (const __half*)v_row, v_row_sb, v_idx, Mc_v, N,
+                                                      (uint64_t)phase, (uint32_t)T_c, angle_mode, sa);
+  else
+    evict_update_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        k_coef, (const __nv_bfloat16*)k_row, k_row_sb, k_idx, Mc_k, v_coef, (const __nv_bfloat16*)v_row, v_row_sb,
+        v_idx, Mc_v, N, (uint64_t)phase, (uint32_t)T_c, angle_mode, sa);
+  FA_CHECK_LAUNCH("fa_evict_step");
   return FA_OK;
 }
 

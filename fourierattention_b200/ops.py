@@ -161,6 +161,32 @@ def cache_step(k_evict, v_evict, kn32, vn32, k_unc_row, v_unc_row, k_new, v_new,
     _count(1)
 
 
+def evict_step(k_coef, k_idx32, v_coef, v_idx32, phase, T_c, angle_mode,
+               k_evict, v_evict, kn32, vn32, k_unc_row, v_unc_row, k_new, v_new, k_dst, v_dst):
+    """``evict_update`` of the evicted row followed by ``cache_step``, as one launch."""
+    _need_cuda(k_evict, k_new, k_dst)
+    B, F = k_evict.shape
+    if k_new.dim() == 4:
+        k_new, v_new = k_new[:, :, 0], v_new[:, :, 0]
+    Hkv, D = k_new.shape[1], k_new.shape[2]
+    if k_new.stride(2) != 1 or v_new.stride() != k_new.stride() or v_evict.stride() != k_evict.stride() \
+            or v_dst.stride() != k_dst.stride():
+        raise ValueError("fa_evict_step: K and V must share strides and have a contiguous last dimension")
+    ref = k_coef if k_coef is not None else v_coef
+    N = ref.shape[1] // 2 if ref is not None else 1
+    with torch.cuda.device(k_evict.device):
+        check(lib.fa_evict_step(_p(k_coef), _p(k_evict) if k_coef is not None else None, k_evict.stride(0),
+                                _p(k_idx32), k_coef.shape[2] if k_coef is not None else 0,
+                                _p(v_coef), _p(v_evict) if v_coef is not None else None, v_evict.stride(0),
+                                _p(v_idx32), v_coef.shape[2] if v_coef is not None else 0,
+                                N, int(phase), int(T_c), int(angle_mode),
+                                _p(k_evict), _p(v_evict), k_evict.stride(0), _p(kn32), kn32.numel(), _p(vn32),
+                                vn32.numel(), _p(k_unc_row), k_unc_row.stride(0), _p(v_unc_row), v_unc_row.stride(0),
+                                _p(k_new), _p(v_new), k_new.stride(0), k_new.stride(1), _p(k_dst), _p(v_dst),
+                                k_dst.stride(0), _dt(k_evict), B, Hkv, D, _stream(k_evict)), "fa_evict_step")
+    _count(1)
+
+
 class DecodeTables:
     """int32 device copies of the eight index vectors the attention kernel reads."""
 

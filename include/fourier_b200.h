@@ -117,6 +117,19 @@ int fa_cache_step(const void* k_evict, const void* v_evict, int64_t evict_sb,
                   void* k_dst, void* v_dst, int64_t dst_sb,
                   int dtype, int B, int Hkv, int D, fa_stream_t stream);
 
+/* fa_evict_update and fa_cache_step of one decode step in a single launch (same arguments, same results:
+ * the two touch disjoint memory).  No separate counterpart in the reference: it is the body of the
+ * steady-state branch of DynamicCache.update (CU:732-743) as one call. */
+int fa_evict_step(float* k_coef, const void* k_row, int64_t k_row_sb, const int32_t* k_idx, int Mc_k,
+                  float* v_coef, const void* v_row, int64_t v_row_sb, const int32_t* v_idx, int Mc_v,
+                  int N, int64_t phase, int T_c, int angle_mode,
+                  const void* k_evict, const void* v_evict, int64_t evict_sb,
+                  const int32_t* kn_idx, int Mn_k, const int32_t* vn_idx, int Mn_v,
+                  void* k_unc, int64_t k_unc_sb, void* v_unc, int64_t v_unc_sb,
+                  const void* k_new, const void* v_new, int64_t new_sb, int64_t new_sh,
+                  void* k_dst, void* v_dst, int64_t dst_sb,
+                  int dtype, int B, int Hkv, int D, fa_stream_t stream);
+
 /* ---- fused decode attention over the compressed cache --------------------------------------
  * Replaces triton_fourier_attn (KM:684-779: kernel KM:470-681 plus the PyTorch split-KV merge
  * KM:756-776) and, in semantics, torch_fourier_attn (KM:794-837).  One query token per sequence.

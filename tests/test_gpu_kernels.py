@@ -321,6 +321,37 @@ def test_evict_update_matches_oracle(mode):
     assert np.abs(host(kd) - wk).max() <= 2e-5 and np.abs(host(vd) - wv).max() <= 2e-5
 
 
+def test_evict_step_equals_the_two_calls():
+    """The fused step launch writes exactly what evict_update followed by cache_step write."""
+    import fourierattention_b200.ops as ops
+    rng = np.random.default_rng(19)
+    B, N, Hkv, D, S, W, T = 2, 16, 3, 16, 2, 5, 31995
+    F = Hkv * D
+    kidx = np.sort(rng.choice(F, 30, replace=False)); kn = np.setdiff1d(np.arange(F), kidx)
+    vidx = np.sort(rng.choice(F, 17, replace=False)); vn = np.setdiff1d(np.arange(F), vidx)
+    i32 = lambda a: dev(a.astype(np.int32))
+    state = lambda: dict(
+        kc=dev(rng.standard_normal((B, 2 * N, 30)).astype(np.float32) * 50),
+        vc=dev(rng.standard_normal((B, 2 * N, 17)).astype(np.float32) * 50),
+        kbuf=dev(fo.rnd(rng.standard_normal((B, S + 2 * W, F)).astype(np.float32), "bf16"), "bf16"),
+        vbuf=dev(fo.rnd(rng.standard_normal((B, S + 2 * W, F)).astype(np.float32), "bf16"), "bf16"),
+        kunc=torch.zeros((B, 4, 24), dtype=torch.bfloat16, device="cuda"),
+        vunc=torch.zeros((B, 4, 32), dtype=torch.bfloat16, device="cuda"))
+    a = state()
+    b_ = {k: v.clone() for k, v in a.items()}
+    knew = dev(fo.rnd(rng.standard_normal((B, Hkv, 1, D)).astype(np.float32), "bf16"), "bf16")
+    vnew = dev(fo.rnd(rng.standard_normal((B, Hkv, 1, D)).astype(np.float32), "bf16"), "bf16")
+    row = S + 1
+    ops.evict_update(a["kc"], a["kbuf"][:, row], i32(kidx), a["vc"], a["vbuf"][:, row], i32(vidx), 777, T, ops.ANGLE_KM57)
+    ops.cache_step(a["kbuf"][:, row], a["vbuf"][:, row], i32(kn), i32(vn), a["kunc"][:, 2, :len(kn)],
+                   a["vunc"][:, 2, :len(vn)], knew, vnew, a["kbuf"][:, row + W], a["vbuf"][:, row + W])
+    ops.evict_step(b_["kc"], i32(kidx), b_["vc"], i32(vidx), 777, T, ops.ANGLE_KM57, b_["kbuf"][:, row],
+                   b_["vbuf"][:, row], i32(kn), i32(vn), b_["kunc"][:, 2, :len(kn)], b_["vunc"][:, 2, :len(vn)],
+                   knew, vnew, b_["kbuf"][:, row + W], b_["vbuf"][:, row + W])
+    for k in a:
+        assert torch.equal(a[k], b_[k]), k
+
+
 def test_errors_are_python_exceptions():
     import fourierattention_b200.ops as ops
     x = torch.zeros((1, 4, 8), dtype=torch.float32, device="cuda")
