@@ -83,7 +83,7 @@ def span_slice(n_rows, rank, world):
 
 class _LayerState:
     __slots__ = ("compressed", "kbuf", "vbuf", "off", "k_unc", "v_unc", "n_mid", "k_coef", "v_coef",
-                 "stats32", "local_len", "mid_l0")
+                 "stats32", "local_len", "mid_l0", "calls")
 
 
 class DynamicCache(Cache):
@@ -254,6 +254,11 @@ class DynamicCache(Cache):
         else:
             raise NotImplementedError("layers must be cached in order")
         st.stats32 = tuple(t.to(torch.float32).contiguous() for t in (k_ua, k_ia, k_scale, v_ua, v_ia, v_scale))
+        owner = self.seq_shard is None or self.seq_shard[0] == 0      # the rank that attends sinks + window
+        st.calls = ops.LayerCalls(st.kbuf, st.vbuf, st.k_unc, st.v_unc,
+                                  k_coef if tb.kc_list.numel() else None, v_coef if tb.vc_list.numel() else None,
+                                  st.stats32, tb, S, W, self.heads, self.attention_period, st.mid_l0,
+                                  compress_period(self.attention_period), self.update_angle, with_il=owner)
         self.curr_tokennum[layer_idx] += n_mid                          # cache_utils_fourier.py:593
         return st
 
@@ -342,27 +347,15 @@ class DynamicCache(Cache):
             raise NotImplementedError("window growth after a compressed prefill (cache_utils_fourier.py:681-729) "
                                       "is not supported: it needs n_mid + batch + 1 <= maxlocallen")
         S, W = self.numinittokens, self.maxlocallen
-        tb = self._tables[layer_idx]
-        T_c = compress_period(self.attention_period)
         self.curr_tokennum[layer_idx] += 1                        # incremented before use (cache_utils_fourier.py:732)
         phase = self.curr_tokennum[layer_idx]
-        row = S + st.off
-        k_ev, v_ev = st.kbuf[:, row], st.vbuf[:, row]
-        appends = self.seq_shard is None or self.seq_shard[0] == self.seq_shard[1] - 1
+        appends = self.seq_shard is None or self.seq_shard[0] == self.seq_shard[1] - 1   # else another rank stores the row
         if appends and st.n_mid + 1 > st.k_unc.shape[1]:
             grow = lambda b: torch.cat([b, torch.empty_like(b)], dim=1)
             st.k_unc, st.v_unc = grow(st.k_unc), grow(st.v_unc)
-        if appends:
-            k_unc_row, v_unc_row = st.k_unc[:, st.n_mid], st.v_unc[:, st.n_mid]
-            kn, vn = tb.kn_list, tb.vn_list
-        else:                                                    # another rank stores the evicted row
-            k_unc_row, v_unc_row = st.k_unc[:, 0], st.v_unc[:, 0]
-            kn = vn = tb.kn_list[:0]
+            st.calls.rebind(st.k_unc, st.v_unc)
         # eviction into the coefficients, verbatim append and window slide in one launch
-        ops.evict_step(st.k_coef if tb.kc_list.numel() else None, tb.kc_list,
-                       st.v_coef if tb.vc_list.numel() else None, tb.vc_list, phase, T_c, self.update_angle,
-                       k_ev, v_ev, kn, vn, k_unc_row, v_unc_row, key_states, value_states,
-                       st.kbuf[:, row + W], st.vbuf[:, row + W])
+        st.calls.step(st.off, st.n_mid if appends else 0, phase, key_states, value_states, appends)
         if appends:
             st.n_mid += 1
         st.off += 1
@@ -384,30 +377,14 @@ class DynamicCache(Cache):
         st = self._state[layer_idx]
         if not st.compressed:
             raise RuntimeError("layer is not compressed; use dense attention on k_local / v_local")
-        S, W = self.numinittokens, self.maxlocallen
-        tb = self._tables[layer_idx]
-        Mn_k, Mn_v = tb.kn_list.numel(), tb.vn_list.numel()
-        lo = S + st.off
-        owner = self.seq_shard is None or self.seq_shard[0] == 0
-        k_sink = st.kbuf[:, :S] if (owner and S > 0) else None
-        v_sink = st.vbuf[:, :S] if (owner and S > 0) else None
-        k_win = st.kbuf[:, lo:lo + W] if owner else None
-        v_win = st.vbuf[:, lo:lo + W] if owner else None
-        k_mn = st.k_unc[:, :st.n_mid, :Mn_k] if st.n_mid else None
-        v_mn = st.v_unc[:, :st.n_mid, :Mn_v] if st.n_mid else None
         q = query if query.dim() == 2 else query[:, 0]
         B = q.shape[0]
         D = q.shape[1] // num_head_q
-        a = st.stats32
         if self.seq_shard is None:
-            out = ops.decode_attn(q, k_sink, v_sink, k_win, v_win, k_mn, v_mn, st.k_coef, st.v_coef,
-                                  a[0], a[1], a[2], a[3], a[4], a[5], tb, num_head_q, self.heads,
-                                  self.attention_period, sm_scale, st.mid_l0, phase_events=phase_events)
+            out = st.calls.attend(q, st.off, st.n_mid, num_head_q, sm_scale, phase_events)
             return out.view(B, num_head_q, 1, D)
         import torch.distributed as dist
-        out, m, l = ops.decode_attn(q, k_sink, v_sink, k_win, v_win, k_mn, v_mn, st.k_coef, st.v_coef,
-                                    a[0], a[1], a[2], a[3], a[4], a[5], tb, num_head_q, self.heads,
-                                    self.attention_period, sm_scale, st.mid_l0, return_lse=True)
+        out, m, l = st.calls.attend(q, st.off, st.n_mid, num_head_q, sm_scale, return_lse=True)
         world = self.seq_shard[1]
         rows = B * num_head_q
         pack = torch.cat([out.view(rows, D), m.view(rows, 1), l.view(rows, 1)], dim=1)
