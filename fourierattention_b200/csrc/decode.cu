@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_prepare_kernel(const __gri
     for (int r = 0; r < R_MAX; ++r) acc[r] = 0.f;
     const float* cr = a.k_coef + ((int64_t)b * 2 * N + row) * Mc + ca;
     if (vec) {
-#pragma unroll 4
+#pragma unroll 8
       for (int i = 0; i < len; i += 4) {
         const float4 cv = __ldg(reinterpret_cast<const float4*>(cr + i));
 #pragma unroll
@@ -760,7 +760,7 @@ __host__ __device__ inline int finish_smem_bytes(int NCH, int N, int D) {
   return (rup(NCH, 4) + 2 * N + rup(D, 4) + 4 * FIN_THREADS) * 4;
 }
 
-__global__ void __launch_bounds__(FIN_THREADS) decode_finish_kernel(const __grid_constant__ DecodeParams p) {
+__global__ void __launch_bounds__(FIN_THREADS, 2) decode_finish_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const fa_decode_args_t& a = p.a;
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
@@ -772,49 +772,104 @@ __global__ void __launch_bounds__(FIN_THREADS) decode_finish_kernel(const __grid
   float* red = O + rup(D, 4);                       // [FIN_THREADS][4]
   __shared__ float s_L, s_P, s_ms;
   const int g = h / R;
-  if (tid < 32) {
-    float ms = NEG_BIG;
-    for (int i = tid; i < NCH; i += 32) {
-      const int64_t o = ((int64_t)b * NCH + i) * Hq + h;
-      if (p.l_part[o] > 0.f) ms = fmaxf(ms, p.m_part[o]);
+  float P, L, ms_all;
+  if (NCH <= 32) {
+    // Few chunk slots: every warp works the merge weights out for itself (lane i <-> slot i) while the
+    // loads of the partial results it is going to merge are already in flight; nothing waits on a barrier.
+    const int lane = tid & 31;
+    float li = 0.f, mi = NEG_BIG;
+    if (lane < NCH) {
+      const int64_t o = ((int64_t)b * NCH + lane) * Hq + h;
+      li = p.l_part[o];
+      mi = p.m_part[o];
     }
-    ms = warp_max(ms);
-    float Ls = 0.f, Ps = 0.f;
-    for (int i = tid; i < NCH; i += 32) {
-      const int64_t o = ((int64_t)b * NCH + i) * Hq + h;
-      const float l = p.l_part[o];
-      const float w = (l > 0.f) ? exp2f(p.m_part[o] - ms) : 0.f;
-      aw[i] = w;
-      Ls = fmaf(w, l, Ls);
-      if (i >= p.n_il_chunks) Ps = fmaf(w, l, Ps);
+    float pv[32];   // this thread's partial results, first of g, then of the verbatim numerators
+    const bool has_n = mid && tid < 2 * N, has_d = tid < D;
+    const float* gp = p.g_part + ((int64_t)b * NM * Hq + h) * 2 * N + tid;
+    const float* op = p.o_part + ((int64_t)b * NCH * Hq + h) * D + tid;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) pv[i] = (has_n && i < NM) ? gp[(int64_t)i * Hq * 2 * N] : 0.f;
+    const float ms = warp_max(li > 0.f ? mi : NEG_BIG);
+    const float wi = li > 0.f ? exp2f(mi - ms) : 0.f;
+    L = warp_sum(wi * li);
+    P = warp_sum(lane >= p.n_il_chunks ? wi * li : 0.f);
+    ms_all = ms;
+    float gacc = 0.f, oacc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float w_mid = __shfl_sync(0xffffffffu, wi, (p.n_il_chunks + i) & 31);
+      gacc = fmaf(i < NM ? w_mid : 0.f, pv[i], gacc);
     }
-    Ls = warp_sum(Ls);
-    Ps = warp_sum(Ps);
-    if (tid == 0) {
-      s_L = Ls;
-      s_P = Ps;
-      s_ms = ms;
+    if (tid < 32 * ((D + 31) / 32)) {   // whole warps, so that the shuffles stay converged
+#pragma unroll
+      for (int i = 0; i < 32; ++i) pv[i] = (has_d && i < NCH) ? op[(int64_t)i * Hq * D] : 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) oacc = fmaf(__shfl_sync(0xffffffffu, wi, i), pv[i], oacc);
     }
-  }
-  __syncthreads();
-  if (mid) {
-    for (int n = tid; n < 2 * N; n += FIN_THREADS) {
-      const float* gp = p.g_part + ((int64_t)b * NM * Hq + h) * 2 * N + n;
+    if (has_n) Gs[tid] = gacc;
+    if (has_d) O[tid] = oacc;
+    if (mid) {
+      for (int n = tid + FIN_THREADS; n < 2 * N; n += FIN_THREADS) {   // 2N > 512 only
+        const float* gp = p.g_part + ((int64_t)b * NM * Hq + h) * 2 * N + n;
+        float acc = 0.f;
+        for (int i = 0; i < NM; ++i) acc = fmaf(__shfl_sync(0xffffffffu, wi, (p.n_il_chunks + i) & 31), gp[(int64_t)i * Hq * 2 * N], acc);
+        Gs[n] = acc;
+      }
+    }
+    for (int d = tid + FIN_THREADS; d < D; d += FIN_THREADS) {           // D > 512 only
+      const float* op = p.o_part + ((int64_t)b * NCH * Hq + h) * D + d;
       float acc = 0.f;
-#pragma unroll 4
-      for (int i = 0; i < NM; ++i) acc = fmaf(aw[p.n_il_chunks + i], gp[(int64_t)i * Hq * 2 * N], acc);
-      Gs[n] = acc;
+      for (int i = 0; i < NCH; ++i) acc = fmaf(__shfl_sync(0xffffffffu, wi, i), op[(int64_t)i * Hq * D], acc);
+      O[d] = acc;
     }
-  }
-  for (int d = tid; d < D; d += FIN_THREADS) {
-    const float* op = p.o_part + ((int64_t)b * NCH * Hq + h) * D + d;
-    float acc = 0.f;
-#pragma unroll 4
-    for (int i = 0; i < NCH; ++i) acc = fmaf(aw[i], op[(int64_t)i * Hq * D], acc);
-    O[d] = acc;
+  } else {
+    if (tid < 32) {
+      float ms = NEG_BIG;
+      for (int i = tid; i < NCH; i += 32) {
+        const int64_t o = ((int64_t)b * NCH + i) * Hq + h;
+        if (p.l_part[o] > 0.f) ms = fmaxf(ms, p.m_part[o]);
+      }
+      ms = warp_max(ms);
+      float Ls = 0.f, Ps = 0.f;
+      for (int i = tid; i < NCH; i += 32) {
+        const int64_t o = ((int64_t)b * NCH + i) * Hq + h;
+        const float l = p.l_part[o];
+        const float w = (l > 0.f) ? exp2f(p.m_part[o] - ms) : 0.f;
+        aw[i] = w;
+        Ls = fmaf(w, l, Ls);
+        if (i >= p.n_il_chunks) Ps = fmaf(w, l, Ps);
+      }
+      Ls = warp_sum(Ls);
+      Ps = warp_sum(Ps);
+      if (tid == 0) {
+        s_L = Ls;
+        s_P = Ps;
+        s_ms = ms;
+      }
+    }
+    __syncthreads();
+    if (mid) {
+      for (int n = tid; n < 2 * N; n += FIN_THREADS) {
+        const float* gp = p.g_part + ((int64_t)b * NM * Hq + h) * 2 * N + n;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int i = 0; i < NM; ++i) acc = fmaf(aw[p.n_il_chunks + i], gp[(int64_t)i * Hq * 2 * N], acc);
+        Gs[n] = acc;
+      }
+    }
+    for (int d = tid; d < D; d += FIN_THREADS) {
+      const float* op = p.o_part + ((int64_t)b * NCH * Hq + h) * D + d;
+      float acc = 0.f;
+#pragma unroll 8
+      for (int i = 0; i < NCH; ++i) acc = fmaf(aw[i], op[(int64_t)i * Hq * D], acc);
+      O[d] = acc;
+    }
+    __syncthreads();   // s_L, s_P, s_ms are read below
+    P = s_P;
+    L = s_L;
+    ms_all = s_ms;
   }
   __syncthreads();
-  const float P = s_P, L = s_L;
   const int c0 = mid ? a.vc_h[g] : 0, c1 = mid ? a.vc_h[g + 1] : 0;
   const bool vec = (Mc & 3) == 0;   // coefficient rows start on 16-byte boundaries
   const int W = vec ? 4 : 1;
@@ -859,7 +914,7 @@ __global__ void __launch_bounds__(FIN_THREADS) decode_finish_kernel(const __grid
   const float inv = poisoned ? __int_as_float(0x7fc00000) : 1.0f / L;
   for (int d = tid; d < D; d += FIN_THREADS) a.out[((int64_t)b * Hq + h) * D + d] = O[d] * inv;
   if (tid == 0) {
-    if (a.m_out) a.m_out[(int64_t)b * Hq + h] = s_ms;
+    if (a.m_out) a.m_out[(int64_t)b * Hq + h] = ms_all;
     if (a.l_out) a.l_out[(int64_t)b * Hq + h] = L;
   }
 }
