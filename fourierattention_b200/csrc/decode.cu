@@ -53,6 +53,7 @@ struct DecodeParams {
   int smem_main, smem_prepare;
   int force_exact;     // debugging / testing aid: never pick the tensor-core pass
   int fast, fNT, fNH;  // tensor-core middle-span pass: column tiles of 8 heads, halves per super-tile
+  int wsSEQ, wsNTs;    // warp-specialised form: sequences per CTA, column tiles per sequence
   // scratch
   float *w, *cst, *m_part, *l_part, *o_part, *g_part;
   int* err;  // set by a kernel whose bounded wait gave up; the output kernel then poisons the result
@@ -736,13 +737,18 @@ __global__ void __launch_bounds__(WS_T, 1) decode_main_ws_kernel(const __grid_co
 #ifdef FA_PHASE_TIMING
   const long long cta_t0 = clock64();
 #endif
-  if ((int)blockIdx.x < p.n_il_chunks) {
-    il_chunk_mma<T>(p, b, blockIdx.x, smem_raw);
+  // blockIdx.y is a group of wsSEQ sequences: first the sinks+window CTAs of each of them, then the group's
+  // middle-span CTAs
+  const int n_il_ctas = p.wsSEQ * p.n_il_chunks;
+  if ((int)blockIdx.x < n_il_ctas) {
+    const int seq = blockIdx.x / p.n_il_chunks, chunk = blockIdx.x - seq * p.n_il_chunks;
+    if (b * p.wsSEQ + seq >= p.a.B) return;
+    il_chunk_mma<T>(p, b * p.wsSEQ + seq, chunk, smem_raw);
 #ifdef FA_PHASE_TIMING
     if (threadIdx.x == 0) atomicAdd(&g_phase_clk[14], (unsigned long long)(clock64() - cta_t0));
 #endif
   } else {
-    mid_chunk_ws<T>(p, b, blockIdx.x - p.n_il_chunks, smem_raw);
+    mid_chunk_ws<T>(p, b * p.wsSEQ, blockIdx.x - n_il_ctas, smem_raw);
 #ifdef FA_PHASE_TIMING
     if (threadIdx.x == 256) atomicAdd(&g_phase_clk[15], (unsigned long long)(clock64() - cta_t0));
 #endif
@@ -975,6 +981,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
   int mid_smem_bytes = 0, il_smem_fast = 0;
   p.J = 8; p.kvh = 1; p.HG = p.R; p.HGp = 8; p.n_groups = 1; p.pitchK = p.pitchV = 16; p.qpitch = 4;
   p.n_mid_chunks = 0; p.mid_chunk = 8;
+  p.fast = 0; p.fNT = 1; p.fNH = 1; p.wsSEQ = 1; p.wsNTs = 1; p.TRm = 16; p.il_tpc = 1;
   if (a.n_mid > 0) {
     FA_REQUIRE(a.N > 0 && a.T > 0, FA_ERR_SHAPE, "fa_decode_attn: N and T must be positive");
     FA_REQUIRE(a.N <= 1024, FA_ERR_CAPACITY, "fa_decode_attn: N (%d) exceeds 1024", a.N);
@@ -1009,6 +1016,8 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
     // 64-token super-tile (interpolation through 16 nodes is then exact to ~1e-7) and the shape fits
     // its register / shared-memory tiling; otherwise the exact CUDA-core pass above is used
     p.fast = 0;
+    p.wsSEQ = 1;
+    p.wsNTs = 1;
     {
       const int NT = ceil_div(a.Hq, 8);
       auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
@@ -1045,9 +1054,19 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
           const int mtv0 = a.vn_h_host[g0] >> 4, mtvn = ((a.vn_h_host[g1 + 1] + 15) >> 4) - mtv0;
           if ((kc1 - kc0) / 16 > WS_KS || mtvn > WS_MTV) ok = false;
         }
-        const WsSmem L = ws_smem(a.N, a.Mn_k, a.Mn_v);
+        // sequences per CTA: as many as fill the four column tiles (and the 32 lanes that issue their boxes)
+        int seq = FNT_MAX / NT;
+        if (seq > a.B) seq = a.B;
+        const int nbK = ceil_div(a.Mn_k, 64), nbV = ceil_div(a.Mn_v, 64);
+        while (seq > 1 && (seq * (nbK > nbV ? nbK : nbV) > 32 ||
+                           ws_smem(a.N, seq * nbK * 64, seq * nbV * 64).total > 227 * 1024))
+          --seq;
+        const WsSmem L = ws_smem(a.N, seq * nbK * 64, seq * nbV * 64);
         if (ok && L.total <= 227 * 1024) {
           p.fast = 2;
+          p.wsSEQ = seq;
+          p.wsNTs = NT;
+          p.fNT = seq * NT;
           mid_smem_bytes = L.total;
         }
       }
@@ -1058,14 +1077,17 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
       // One wave of CTAs per launch.  Split the CTAs of a sequence between sinks+window rows and the
       // middle span so that the slowest CTA is as short as possible; costs in clock ticks as measured
       // on B200 (cost_il_row per sinks+window row, cost_mid_tok per middle-span token, plus set-up).
-      const int per_seq = sms / a.B > 2 ? sms / a.B : 2;
+      // (the warp-specialised kernel serves wsSEQ sequences per middle-span CTA: count CTAs per such group)
+      const int seqs = p.fast == 2 ? p.wsSEQ : 1;
+      const int per_seq = sms / ceil_div(a.B, seqs) > 2 * seqs ? sms / ceil_div(a.B, seqs) : 2 * seqs;
       const double cost_il_row = 450.0, cost_mid_tok = p.fast == 2 ? 125.0 : 142.0;
       const int n_tiles = ceil_div(a.n_sink, p.TRm) + ceil_div(a.n_win, p.TRm);
       double best = 1e30;
       int best_il = 1;
       for (int n_il = 1; n_il < per_seq && n_il <= n_tiles; ++n_il) {
         const int tpc = ceil_div(n_tiles, n_il);
-        int n_mid = per_seq - ceil_div(n_tiles, tpc);
+        int n_mid = per_seq - seqs * ceil_div(n_tiles, tpc);
+        if (n_mid < 1) break;
         if (n_mid > max_chunks) n_mid = max_chunks;
         const int mid_tok = rup(ceil_div(a.n_mid, n_mid), J);
         const double t_il = 8000.0 + cost_il_row * tpc * p.TRm, t_mid = 24000.0 + cost_mid_tok * mid_tok;
@@ -1080,6 +1102,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
       p.il_chunk_rows = p.il_tpc * p.TRm;
     }
     int target = ((p.fast ? 1 : 3) * sms) / (a.B * p.n_groups) - p.n_il_chunks;
+    if (p.fast == 2) target = sms / ceil_div(a.B, p.wsSEQ) - p.wsSEQ * p.n_il_chunks;
     if (target < 1) target = 1;
     if (target > max_chunks) target = max_chunks;
     p.mid_chunk = rup(ceil_div(a.n_mid, target), J);
@@ -1136,7 +1159,8 @@ static int launch_decode(const DecodeParams& p, cudaStream_t st) {
   dim3 g2(p.n_il_chunks + p.n_mid_chunks * p.n_groups, a.B);
   if (p.fast == 2) {
     if ((rc = set_smem(decode_main_ws_kernel<T>, p.smem_main)) != FA_OK) return rc;
-    decode_main_ws_kernel<T><<<g2, WS_T, p.smem_main, st>>>(p);
+    const dim3 gw(p.wsSEQ * p.n_il_chunks + p.n_mid_chunks, ceil_div(a.B, p.wsSEQ));
+    decode_main_ws_kernel<T><<<gw, WS_T, p.smem_main, st>>>(p);
   } else if (p.fast) {
 #define FA_FAST_CASE(NT_, NH_)                                                                   \
   if (p.fNT == NT_ && p.fNH == NH_) {                                                            \

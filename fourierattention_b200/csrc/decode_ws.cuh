@@ -22,6 +22,10 @@
 // Registers move with the work: the spectral warps give up registers (setmaxnreg) that the score
 // warps, which hold the g and verbatim-V accumulators, take over.
 //
+// When a sequence has 16 or fewer query heads a CTA takes the column tiles of two or four sequences of the
+// batch (their K/V boxes side by side in a ring slot): the node basis and the interpolation weights are the
+// same for all of them, so narrow head counts do not leave score warps idle.
+//
 // The node set is symmetric about the centre of the super-tile, so the basis table holds the eight
 // nodes right of the centre only and the rotation is taken at the centre (a half-integer position:
 // phases are kept modulo 2T).
@@ -95,17 +99,22 @@ __device__ __forceinline__ uint32_t pack_pair(T a, T b) {
 }
 
 template <typename T>
-__device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned char* smem) {
+__device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned char* smem) {
   constexpr int J = 128, HN = 32;
   constexpr bool kBf16 = !std::is_same<T, __half>::value;
   const fa_decode_args_t& a = p.a;
   const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
   const int gq = lane >> 2, tq = lane & 3;
   const int N = a.N, D = a.D, R = p.R, Hq = a.Hq, Mn_k = a.Mn_k, Mn_v = a.Mn_v;
-  const int NT = p.fNT;
+  // A CTA serves `nseq` sequences at once when a sequence has few heads: column tile nt belongs to sequence
+  // b0 + nt / NTs and is that sequence's tile nt % NTs; the node basis is the same for all of them.
+  const int NTs = p.wsNTs;
+  const int nseq = min(p.wsSEQ, a.B - b0);
+  const int NT = nseq * NTs;
   const uint32_t T2 = 2u * (uint32_t)a.T;
   const float inv_T = 1.0f / (float)a.T;
-  const WsSmem L = ws_smem(N, Mn_k, Mn_v);
+  // a ring slot holds the 64-column boxes of all wsSEQ sequences side by side
+  const WsSmem L = ws_smem(N, p.wsSEQ * ((Mn_k + 63) / 64) * 64, p.wsSEQ * ((Mn_v + 63) / 64) * 64);
   float* ec = reinterpret_cast<float*>(smem + L.ec);
   float* es = reinterpret_cast<float*>(smem + L.es);
   __half* fnt = reinterpret_cast<__half*>(smem + L.fnt);
@@ -133,7 +142,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
   const int nst = (l1 - l0 + J - 1) / J;
   const int n_tiles = 4 * nst;   // per super-tile: K half 0, K half 1, V half 0, V half 1
   const int nbK = (Mn_k + 63) / 64, nbV = (Mn_v + 63) / 64;
-  const int64_t slot_id = (int64_t)b * p.NCH + p.n_il_chunks + chunk;
+  auto slot_of = [&](int bb) { return (int64_t)bb * p.NCH + p.n_il_chunks + chunk; };
 
   // called by a whole warp: request half tile i into ring slot i % 3
   auto issue_tile = [&](int i) {
@@ -142,9 +151,12 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
     const int lf = l0 + (i >> 2) * J + (r & 1) * FH;
     const bool is_v = r >= 2;
     const int nb = is_v ? nbV : nbK;
-    if (lane == 0) mbar_expect_tx(full_slot + s, (uint32_t)nb * 8192u);
+    if (lane == 0) mbar_expect_tx(full_slot + s, (uint32_t)(nseq * nb) * 8192u);
     __syncwarp();
-    if (lane < nb) tma_box(slots + s * L.slot_bytes + lane * 8192, is_v ? &p.tm_v : &p.tm_k, 64 * lane, lf, b, full_slot + s);
+    if (lane < nseq * nb) {   // the boxes of sequence 0, then those of sequence 1, ...
+      const int sq = lane / nb, bx = lane - sq * nb;
+      tma_box(slots + s * L.slot_bytes + lane * 8192, is_v ? &p.tm_v : &p.tm_k, 64 * bx, lf, b0 + sq, full_slot + s);
+    }
   };
 
   // ---- set-up (all warps) ---------------------------------------------------------------------
@@ -201,8 +213,10 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
     const int nt1 = wp & 3, khalf = wp >> 2;
     // this chunk's verbatim-V partial starts from zero (the score warps add into it at the end)
     {
-      float* ob = p.o_part + slot_id * Hq * D;
-      for (int e = tid; e < Hq * D; e += 256) ob[e] = 0.f;
+      for (int sq = 0; sq < nseq; ++sq) {
+        float* ob = p.o_part + slot_of(b0 + sq) * Hq * D;
+        for (int e = tid; e < Hq * D; e += 256) ob[e] = 0.f;
+      }
     }
     // w as persistent B fragments (hi / lo): k = frequency row, n = head; this warp holds column
     // tile nt1 for half `khalf` of the 2N rows
@@ -210,8 +224,8 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
     const int kh_steps = (ktot + 1) / 2;
     uint32_t bhi[KH][2], blo[KH][2];
     {
-      const float* wb = p.w + (int64_t)b * Hq * 2 * N;
-      const int h = 8 * nt1 + gq;
+      const float* wb = p.w + (int64_t)(b0 + nt1 / NTs) * Hq * 2 * N;
+      const int h = 8 * (nt1 % NTs) + gq;
 #pragma unroll
       for (int i = 0; i < KH; ++i) {
         const int k0 = 16 * (khalf * kh_steps + i);
@@ -351,13 +365,15 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
 #endif
   const int qw = wp - 8, nt = qw & 3, half = qw >> 2;
   const bool act = nt < NT;
+  const int sq = act ? nt / NTs : 0, ntl = nt - sq * NTs;   // sequence of this column tile, tile within the sequence
+  const int bb = b0 + sq;
   const int v_issuer = NT > 1 ? 1 : 0;   // column tile whose warp refills V slots (tile 0's warp refills K slots)
   __half* pw16 = reinterpret_cast<__half*>(smem + L.pw) + qw * 8 * 72;   // this warp's probabilities
   T* pwT = reinterpret_cast<T*>(pw16);
   // column ranges of this warp's heads in the verbatim stores
   int kc0 = 0, kc1 = 0, mtv0 = 0, mtvn = 0;
   if (act) {
-    const int g0 = (8 * nt) / R, g1 = (min(Hq, 8 * nt + 8) - 1) / R;
+    const int g0 = (8 * ntl) / R, g1 = (min(Hq, 8 * ntl + 8) - 1) / R;
     kc0 = a.kn_h[g0] & ~15;
     kc1 = (a.kn_h[g1 + 1] + 15) & ~15;
     mtv0 = a.vn_h[g0] >> 4;
@@ -368,8 +384,8 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
   // scale is applied to the fp32 sums)
   uint32_t bq[WS_KS][2];
   {
-    const T* q = reinterpret_cast<const T*>(a.q) + (int64_t)b * a.q_sb;
-    const int h = 8 * nt + gq;
+    const T* q = reinterpret_cast<const T*>(a.q) + (int64_t)bb * a.q_sb;
+    const int h = 8 * ntl + gq;
     const int g = h / R;
     int c_lo = 0, c_hi = 0;
     if (act && h < Hq) {
@@ -388,9 +404,12 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
       }
     }
   }
-  const int hc0 = 8 * nt + 2 * tq;   // this thread's two head columns
-  const float cst0 = (act && hc0 < Hq) ? p.cst[(int64_t)b * Hq + hc0] : 0.f;
-  const float cst1 = (act && hc0 + 1 < Hq) ? p.cst[(int64_t)b * Hq + hc0 + 1] : 0.f;
+  const int hc0 = 8 * nt + 2 * tq;    // this thread's two columns among the CTA's 32
+  const int hl0 = 8 * ntl + 2 * tq;   // ... and the heads of sequence bb they stand for
+  const float cst0 = (act && hl0 < Hq) ? p.cst[(int64_t)bb * Hq + hl0] : 0.f;
+  const float cst1 = (act && hl0 + 1 < Hq) ? p.cst[(int64_t)bb * Hq + hl0 + 1] : 0.f;
+  // first column of this sequence's boxes inside a K / V ring slot
+  const int cbK = sq * nbK * 64, cbV = sq * nbV * 64;
   float m_run0 = NEG_BIG, m_run1 = NEG_BIG, lsum0 = 0.f, lsum1 = 0.f;
   float Gacc[4][4][4];
 #pragma unroll
@@ -431,7 +450,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
 #pragma unroll
           for (int mt = 0; mt < 4; ++mt) {
             uint32_t af[4];
-            ldsm_x4(af, ks_ + sw_off(16 * mt + lds_a_row(lane), (kc0 + 16 * ks + lds_a_col(lane)) >> 3));
+            ldsm_x4(af, ks_ + sw_off(16 * mt + lds_a_row(lane), (cbK + kc0 + 16 * ks + lds_a_col(lane)) >> 3));
             mma16816<T>(sc[mt], af, bq[ks]);
           }
         }
@@ -607,7 +626,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
 #pragma unroll
         for (int i = 0; i < WS_MTV; ++i)
           if (i < mtvn)
-            ldsm_x4_t(af[i], vs_ + sw_off(16 * ks + lds_at_row(lane), (16 * (mtv0 + i) + lds_at_col(lane)) >> 3));
+            ldsm_x4_t(af[i], vs_ + sw_off(16 * ks + lds_at_row(lane), (cbV + 16 * (mtv0 + i) + lds_at_col(lane)) >> 3));
 #pragma unroll
         for (int i = 0; i < WS_MTV; ++i)
           if (i < mtvn) mma16816<T>(Oacc[i], af[i], bp[ks]);
@@ -714,25 +733,26 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
   }
   __syncthreads();   // the spectral warps have zeroed this chunk's verbatim-V partial
   if (act && half == 0 && gq == 0) {
-    if (hc0 < Hq) {
-      p.m_part[slot_id * Hq + hc0] = m_run0;
-      p.l_part[slot_id * Hq + hc0] = lsum0 + lx[nt * 8 + 2 * tq];
+    const int64_t slot_id = slot_of(bb);
+    if (hl0 < Hq) {
+      p.m_part[slot_id * Hq + hl0] = m_run0;
+      p.l_part[slot_id * Hq + hl0] = lsum0 + lx[nt * 8 + 2 * tq];
     }
-    if (hc0 + 1 < Hq) {
-      p.m_part[slot_id * Hq + hc0 + 1] = m_run1;
-      p.l_part[slot_id * Hq + hc0 + 1] = lsum1 + lx[nt * 8 + 2 * tq + 1];
+    if (hl0 + 1 < Hq) {
+      p.m_part[slot_id * Hq + hl0 + 1] = m_run1;
+      p.l_part[slot_id * Hq + hl0 + 1] = lsum1 + lx[nt * 8 + 2 * tq + 1];
     }
   }
   if (act) {
     // both halves add their numerators (two addends onto zero: the order does not change the sum)
-    float* ob = p.o_part + slot_id * Hq * D;
+    float* ob = p.o_part + slot_of(bb) * Hq * D;
 #pragma unroll
     for (int i = 0; i < WS_MTV; ++i) {
       if (i < mtvn) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int c = 16 * (mtv0 + i) + gq + 8 * (e >> 1);
-          const int h = hc0 + (e & 1);
+          const int h = hl0 + (e & 1);
           if (c < Mn_v && h < Hq) {
             const int g = h / R;
             if (c >= a.vn_h[g] && c < a.vn_h[g + 1]) atomicAdd(ob + h * D + a.vn_list[c] - g * D, Oacc[i][e]);
@@ -741,7 +761,6 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
       }
     }
   }
-  float* gb = p.g_part + (((int64_t)b * p.n_mid_chunks + chunk) * Hq) * 2 * N;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int mt = qw + 8 * i;
@@ -749,10 +768,12 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b, int chunk, unsigned c
 #pragma unroll
       for (int n = 0; n < 4; ++n) {
         if (n < NT) {
+          const int sqn = n / NTs, ntn = n - sqn * NTs;   // sequence and tile-within-sequence of column tile n
+          float* gb = p.g_part + (((int64_t)(b0 + sqn) * p.n_mid_chunks + chunk) * Hq) * 2 * N;
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int row = 16 * mt + gq + 8 * (e >> 1);
-            const int h = 8 * n + 2 * tq + (e & 1);
+            const int h = 8 * ntn + 2 * tq + (e & 1);
             if (row < 2 * N && h < Hq) gb[(int64_t)h * 2 * N + row] = Gacc[i][n][e];
           }
         }

@@ -44,13 +44,16 @@ FAST_CASES = {
     "fast_nothing_verbatim": _geom(B=1, Hq=4, Hkv=2, D=16, W=6, M=16, P=800, ncomp=16, seed=206),
     "fast_nothing_compressed": _geom(B=1, Hq=4, Hkv=2, D=16, W=6, M=16, P=800, ncomp=0, seed=207),
     "fast_llama8b_layer": _geom(B=1, Hq=32, Hkv=8, D=128, S=4, W=128, M=512, P=24000, dtype="bf16", ncomp=96, seed=208),
+    # few heads per sequence: a CTA of the warp-specialised kernel takes four (then one) / two sequences
+    "fast_packed_4seq": _geom(B=5, Hq=8, Hkv=2, D=64, S=4, W=40, M=16, P=900, dtype="bf16", ncomp=40, seed=209),
+    "fast_packed_2seq": _geom(B=3, Hq=16, Hkv=4, D=64, S=2, W=24, M=32, P=1500, ncomp=48, seed=210),
 }
 
 
 # of these, the shapes the warp-specialised form takes (128-token super-tiles, at most 64 verbatim K and V
 # columns per 8 query heads)
 WS_CASES = {"fast_gqa4_bf16", "fast_32heads_fp16", "fast_one_kv_head", "fast_nothing_verbatim",
-            "fast_nothing_compressed", "fast_llama8b_layer"}
+            "fast_nothing_compressed", "fast_llama8b_layer", "fast_packed_4seq", "fast_packed_2seq"}
 
 
 @pytest.mark.parametrize("name", list(FAST_CASES))
