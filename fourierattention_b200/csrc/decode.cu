@@ -1080,7 +1080,9 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
       // (the warp-specialised kernel serves wsSEQ sequences per middle-span CTA: count CTAs per such group)
       const int seqs = p.fast == 2 ? p.wsSEQ : 1;
       const int per_seq = sms / ceil_div(a.B, seqs) > 2 * seqs ? sms / ceil_div(a.B, seqs) : 2 * seqs;
-      const double cost_il_row = 450.0, cost_mid_tok = p.fast == 2 ? 125.0 : 142.0;
+      // a sinks+window tile costs a fixed part (barriers, waits, refill) plus its MMA / softmax work, which
+      // grows with rows x KV heads (7.2 K ticks for 16 rows x 8 heads)
+      const double cost_il_tile = 2500.0 + 37.0 * p.TRm * a.Hkv, cost_mid_tok = p.fast == 2 ? 100.0 : 142.0;
       const int n_tiles = ceil_div(a.n_sink, p.TRm) + ceil_div(a.n_win, p.TRm);
       double best = 1e30;
       int best_il = 1;
@@ -1090,7 +1092,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
         if (n_mid < 1) break;
         if (n_mid > max_chunks) n_mid = max_chunks;
         const int mid_tok = rup(ceil_div(a.n_mid, n_mid), J);
-        const double t_il = 8000.0 + cost_il_row * tpc * p.TRm, t_mid = 24000.0 + cost_mid_tok * mid_tok;
+        const double t_il = 8000.0 + cost_il_tile * tpc, t_mid = 24000.0 + cost_mid_tok * mid_tok;
         const double t = t_il > t_mid ? t_il : t_mid;
         if (t < best) {
           best = t;

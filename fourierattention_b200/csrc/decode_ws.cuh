@@ -72,7 +72,7 @@ __host__ __device__ inline WsSmem ws_smem(int N, int Mn_k, int Mn_v) {
   s.interp_lo = take(128 * 24 * 2);
   s.snode32 = take(2 * FD * 32 * 4);          // partial node scores of the two halves of the 2N rows
   s.snode = take(2 * 2 * 32 * 24 * 2);        // [buffer][hi, lo][head][24]
-  s.pw = take(8 * 8 * 72 * 2);                // per score warp: probabilities [8 heads][64 tokens + 8]
+  s.pw = take(8 * 64 * 8 * 2);                // per score warp: probabilities [64 tokens][8 heads]
   s.ptx = take(2 * 2 * 32 * 24 * 2);          // [buffer][hi, lo][head][24]  probabilities on the nodes
   s.ptp = take(4 * FD * 8 * 4);               // second half's contribution to them, per column tile
   s.alpha = take(2 * 32 * 4);
@@ -368,7 +368,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
   const int sq = act ? nt / NTs : 0, ntl = nt - sq * NTs;   // sequence of this column tile, tile within the sequence
   const int bb = b0 + sq;
   const int v_issuer = NT > 1 ? 1 : 0;   // column tile whose warp refills V slots (tile 0's warp refills K slots)
-  __half* pw16 = reinterpret_cast<__half*>(smem + L.pw) + qw * 8 * 72;   // this warp's probabilities
+  __half* pw16 = reinterpret_cast<__half*>(smem + L.pw) + qw * 64 * 8;   // this warp's probabilities [64 tokens][8 heads]
   T* pwT = reinterpret_cast<T*>(pw16);
   // column ranges of this warp's heads in the verbatim stores
   int kc0 = 0, kc1 = 0, mtv0 = 0, mtvn = 0;
@@ -503,7 +503,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
     WS_TICK(1);
     // ---- softmax over the 128 tokens of the super-tile (both halves agree on the maximum) ----------
     float al0 = 1.f, al1 = 1.f;
-    float pf[4][4];   // probabilities, already rounded to fp16
+    __half2 ph[4][2];   // probabilities rounded to fp16: (head 2tq, 2tq+1) of token rows gq and gq+8 per 16-token tile
     float pt_acc[4] = {0.f, 0.f, 0.f, 0.f};
     const int iV = 4 * st + 2 + half, sV = iV % 3;
     const uint32_t parV = (uint32_t)(iV / 3) & 1u;
@@ -535,22 +535,16 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
 #pragma unroll
       for (int mt = 0; mt < 4; ++mt) {
         const bool ok0 = (tok0 + 16 * mt + gq) < l1, ok1 = (tok0 + 16 * mt + gq + 8) < l1;
-        const __half h0 = __float2half_rn(ok0 ? exp2f(sc[mt][0] - mn0) : 0.f);
-        const __half h1 = __float2half_rn(ok0 ? exp2f(sc[mt][1] - mn1) : 0.f);
-        const __half h2 = __float2half_rn(ok1 ? exp2f(sc[mt][2] - mn0) : 0.f);
-        const __half h3 = __float2half_rn(ok1 ? exp2f(sc[mt][3] - mn1) : 0.f);
-        // B-operand layout [head][token]; the sums use the rounded values
+        ph[mt][0] = __floats2half2_rn(ok0 ? exp2f(sc[mt][0] - mn0) : 0.f, ok0 ? exp2f(sc[mt][1] - mn1) : 0.f);
+        ph[mt][1] = __floats2half2_rn(ok1 ? exp2f(sc[mt][2] - mn0) : 0.f, ok1 ? exp2f(sc[mt][3] - mn1) : 0.f);
+        // token-major [token][8 heads]: a thread's two heads are one 32-bit store, the B operands come back
+        // through ldmatrix.trans; the sums use the rounded values
         const int j0 = 16 * mt + gq;
-        pw16[(2 * tq) * 72 + j0] = h0;
-        pw16[(2 * tq + 1) * 72 + j0] = h1;
-        pw16[(2 * tq) * 72 + j0 + 8] = h2;
-        pw16[(2 * tq + 1) * 72 + j0 + 8] = h3;
-        pf[mt][0] = __half2float(h0);
-        pf[mt][1] = __half2float(h1);
-        pf[mt][2] = __half2float(h2);
-        pf[mt][3] = __half2float(h3);
-        s0 += pf[mt][0] + pf[mt][2];
-        s1 += pf[mt][1] + pf[mt][3];
+        *reinterpret_cast<__half2*>(pw16 + j0 * 8 + 2 * tq) = ph[mt][0];
+        *reinterpret_cast<__half2*>(pw16 + (j0 + 8) * 8 + 2 * tq) = ph[mt][1];
+        const float2 f0 = __half22float2(ph[mt][0]), f1 = __half22float2(ph[mt][1]);
+        s0 += f0.x + f1.x;
+        s1 += f0.y + f1.y;
       }
       lsum0 = lsum0 * al0 + s0;   // this thread's rows only; the lanes are added at the end
       lsum1 = lsum1 * al1 + s1;
@@ -559,7 +553,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
       // ---- project the probabilities onto the nodes: pt[16 x 8] = Interp^T[16 x 64] * P[64 x 8] ------
       uint32_t bp[4][2];
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks) ldsm_x2(bp[ks], pw16 + lds_b_row(lane) * 72 + 16 * ks + lds_b_col(lane));
+      for (int ks = 0; ks < 4; ++ks) ldsm_x2_t(bp[ks], pw16 + (16 * ks + (lane & 15)) * 8);
       {
         float pt2[3][4];
 #pragma unroll
@@ -586,29 +580,35 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
       WS_TICK(5);
       // ---- verbatim-V numerators -------------------------------------------------------------------
       uint32_t bp_lo[4][2];
-      if (kBf16) {
+      if constexpr (kBf16) {
         // an fp16 value splits exactly into two bf16 values, so the verbatim-V GEMM (model dtype)
         // sees the same probabilities as the spectral side and the denominator
+        using T2 = __nv_bfloat162;
+        float2 res[4][2];   // what the bf16 rounding leaves over
         __syncwarp();
 #pragma unroll
         for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
-          for (int e = 0; e < 4; ++e)
-            pwT[(2 * tq + (e & 1)) * 72 + 16 * mt + gq + 8 * (e >> 1)] = from_f32<T>(pf[mt][e]);
-        __syncwarp();
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) ldsm_x2(bp[ks], pwT + lds_b_row(lane) * 72 + 16 * ks + lds_b_col(lane));
-        __syncwarp();
-#pragma unroll
-        for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float hi = to_f32(from_f32<T>(pf[mt][e]));
-            pwT[(2 * tq + (e & 1)) * 72 + 16 * mt + gq + 8 * (e >> 1)] = from_f32<T>(pf[mt][e] - hi);
+          for (int r = 0; r < 2; ++r) {
+            const float2 f = __half22float2(ph[mt][r]);
+            const T2 hi = __floats2bfloat162_rn(f.x, f.y);
+            const float2 hf = __bfloat1622float2(hi);
+            res[mt][r] = make_float2(f.x - hf.x, f.y - hf.y);
+            *reinterpret_cast<T2*>(pwT + (16 * mt + gq + 8 * r) * 8 + 2 * tq) = hi;
           }
         __syncwarp();
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) ldsm_x2(bp_lo[ks], pwT + lds_b_row(lane) * 72 + 16 * ks + lds_b_col(lane));
+        for (int ks = 0; ks < 4; ++ks) ldsm_x2_t(bp[ks], pwT + (16 * ks + (lane & 15)) * 8);
+        __syncwarp();
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+          for (int r = 0; r < 2; ++r)
+            *reinterpret_cast<T2*>(pwT + (16 * mt + gq + 8 * r) * 8 + 2 * tq) =
+                __floats2bfloat162_rn(res[mt][r].x, res[mt][r].y);
+        __syncwarp();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) ldsm_x2_t(bp_lo[ks], pwT + (16 * ks + (lane & 15)) * 8);
       }
       mbar_wait(full_slot + sV, parV, dead, p.err);
       WS_TICK(6);
