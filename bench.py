@@ -240,11 +240,17 @@ def ours_arm(args, w):
             mk = lambda s: torch.randn(s, device=dev, dtype=torch.float32, generator=gen).to(tdt)
         return mk(shape_q), mk(shape_kv), mk(shape_kv)
 
-    def step_device(q, k, v, s, events=None):
+    def step_device(q, k, v, s, events=None, main_only=False):
+        # main_only: record just the two events that bracket the main kernel (the timed steps), so that the
+        # timed region carries as few extra stream operations as the roofline measurement needs
         for layer in range(L):
             cache.update(k[s, layer], v[s, layer], layer)
-            cache.fourier_attention(q[s, layer], layer, hq_l,
-                                    phase_events=events[s][layer] if events is not None else None)
+            ev = None
+            if events is not None:
+                ev = events[s][layer]
+                if main_only:
+                    ev = [None, ev[1], ev[2], None, None] if layer % 4 == 0 else None
+            cache.fourier_attention(q[s, layer], layer, hq_l, phase_events=ev)
 
     def barrier():
         torch.cuda.synchronize()
@@ -260,7 +266,7 @@ def ours_arm(args, w):
             for e in l_:
                 e.record()
     for s in range(W_):
-        step_device(q, k, v, s)
+        step_device(q, k, v, s, events)      # warm-up steps also give the per-call split (all five events)
     sampler = ClockSampler(local)
     sampler.start()
     time.sleep(0.3)
@@ -270,7 +276,7 @@ def ours_arm(args, w):
     wall0 = time.time()
     ev0.record()
     for s in range(W_, W_ + K_):
-        step_device(q, k, v, s, events)
+        step_device(q, k, v, s, events, main_only=True)
     ev1.record()
     barrier()
     wall1 = time.time()
@@ -279,12 +285,15 @@ def ours_arm(args, w):
     ms = ev0.elapsed_time(ev1)
     main_ms, call_ms = [], []
     for s in range(W_, W_ + K_):
-        for layer in range(L):
+        for layer in range(0, L, 4):             # every fourth layer's main kernel is bracketed by events
             e = events[s][layer]
             main_ms.append(e[1].elapsed_time(e[2]))
+    for s in range(1, W_):                       # the whole attention call, from the warm-up steps
+        for layer in range(L):
+            e = events[s][layer]
             call_ms.append(e[0].elapsed_time(e[4]))
     main_avg = sum(main_ms) / len(main_ms)
-    call_avg = sum(call_ms) / len(call_ms)
+    call_avg = sum(call_ms) / len(call_ms) if call_ms else float("nan")
     del q, k, v
 
     # ---- leg 2: end to end through the public API with host buffers --------------------------

@@ -1148,7 +1148,7 @@ static int launch_decode(const DecodeParams& p, cudaStream_t st) {
   const fa_decode_args_t& a = p.a;
   int rc;
   auto mark = [&](int i) {
-    if (a.phase_events_host) cudaEventRecord((cudaEvent_t)a.phase_events_host[i], st);
+    if (a.phase_events_host && a.phase_events_host[i]) cudaEventRecord((cudaEvent_t)a.phase_events_host[i], st);
   };
   mark(0);
   if (a.n_mid > 0) {

@@ -274,7 +274,7 @@ def decode_attn(q, k_sink, v_sink, k_win, v_win, k_mn, v_mn, k_coef, v_coef,
         l = torch.empty_like(m)
         a.m_out, a.l_out = m.data_ptr(), l.data_ptr()
     if phase_events is not None:       # five torch.cuda.Event(enable_timing=True), see fourier_b200.h
-        ev = (C.c_void_p * 5)(*[e.cuda_event for e in phase_events])
+        ev = (C.c_void_p * 5)(*[(e.cuda_event if e is not None else None) for e in phase_events])
         a.phase_events_host = C.cast(ev, C.c_void_p)
     global last_decode_path
     last_decode_path = lib.fa_decode_path(C.byref(a))
@@ -407,7 +407,7 @@ class LayerCalls:
         else:
             a.m_out = a.l_out = None
         if phase_events is not None:
-            ev = (C.c_void_p * 5)(*[e.cuda_event for e in phase_events])
+            ev = (C.c_void_p * 5)(*[(e.cuda_event if e is not None else None) for e in phase_events])
             a.phase_events_host = C.cast(ev, C.c_void_p)
         else:
             a.phase_events_host = None

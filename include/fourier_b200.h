@@ -172,7 +172,7 @@ typedef struct {
   size_t scratch_bytes;
   /* optional profiling aid: a HOST array of five cudaEvent_t recorded on `stream` before the first
    * launch and after each launch (prepare, main; the third and fourth event both follow main, the fifth follows
-   * finish); null = off   */
+   * finish); null = off, and a null entry of the array skips that record   */
   void* const* phase_events_host;
   /* optional HOST copies of kn_h and vn_h (Hkv + 1 entries each); with them the planner can check the
    * per-head column ranges and pick the warp-specialised middle-span pass; null = not given          */
