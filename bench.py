@@ -342,7 +342,7 @@ def ours_arm(args, w):
         kernel_name = {0: "decode_main_kernel", 1: "decode_main_fast_kernel", 2: "decode_main_ws_kernel"}[ops.last_decode_path]
         traffic, traffic_src = None, None
         if fast and world == 1 and args.workload in ("llama31_8b_32k", "profile_small"):
-            traffic = 307.3e6 if ops.last_decode_path == 2 else 303.7e6
+            traffic = 307.7e6 if ops.last_decode_path == 2 else 303.7e6
             traffic_src = "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch of profile_small " \
                           f"(profiles/{kernel_name}.profile_small.md)"
         h2d = L * B * (hq_l * D + 2 * hk * D) * 2
