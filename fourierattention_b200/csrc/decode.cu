@@ -56,7 +56,7 @@ struct DecodeParams {
   int wsSEQ, wsNTs;    // warp-specialised form: sequences per CTA, column tiles per sequence
   // scratch
   float *w, *cst, *m_part, *l_part, *o_part, *g_part;
-  int* err;  // set by a kernel whose bounded wait gave up; the output kernel then poisons the result
+  int* err;  // set by a kernel whose bounded wait gave up; the finish kernel then poisons the result
   int64_t scratch_floats;
 };
 

@@ -97,7 +97,7 @@ __device__ __forceinline__ void mbar_expect_tx(void* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 // Bounded wait: gives up after ~2e9 clock ticks (about a second), records the failure in *dead (shared,
-// makes every later wait of the CTA return at once) and in *err (global, read by the output kernel),
+// makes every later wait of the CTA return at once) and in *err (global, read by the finish kernel),
 // and lets the caller carry on so that no thread is left behind at a barrier.
 __device__ __forceinline__ void mbar_wait(void* bar, uint32_t parity, volatile int* dead, int* err) {
   if (*dead) return;
