@@ -264,11 +264,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
       if (j >= 2) mbar_wait(empty_sp + buf, ((j >> 1) - 1) & 1, dead, p.err);
       WS_TICK(10);
       // ---- node basis: rotate the table to this super-tile's centre ------------------------------
-#ifdef WS_EXPERIMENT_NO_S
-      if (false) {
-#else
       if (2 * np < N) {
-#endif
         float rc[2], rs[2];
 #pragma unroll
         for (int f = 0; f < 2; ++f) {
@@ -299,11 +295,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
       ws_group_sync(1);
       WS_TICK(11);
       // ---- scores at the nodes: s_node[16 x HN] = Fn_t[16 x 2N] * w[2N x HN] -----------------------
-#ifdef WS_EXPERIMENT_NO_S
-      if (false) {
-#else
       if (nt1 < NT) {
-#endif
         // consecutive MMAs never share an accumulator: a dependent MMA would wait out the whole latency
         // of the one before it
         float acc[6][4];
