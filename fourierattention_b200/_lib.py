@@ -18,7 +18,9 @@ STATUS_NAMES = {0: "FA_OK", -1: "FA_ERR_NULL", -2: "FA_ERR_SHAPE", -3: "FA_ERR_D
 # every symbol include/fourier_b200.h declares
 EXPORTS = ["fa_version", "fa_last_error_string", "fa_gather_cols", "fa_colstats", "fa_compress_scratch_bytes",
            "fa_compress", "fa_evict_update", "fa_recon_stats_scratch_bytes", "fa_recon_stats", "fa_fourier_inverse",
-           "fa_cache_step", "fa_evict_step", "fa_decode_scratch_bytes", "fa_decode_path", "fa_decode_attn", "fa_decode_attn_static", "fa_merge"]
+           "fa_cache_step", "fa_evict_step", "fa_decode_scratch_bytes", "fa_decode_path", "fa_decode_attn", "fa_decode_attn_static", "fa_merge",
+           "fa_layer_create", "fa_layer_destroy", "fa_layer_rebind_stores", "fa_layer_update", "fa_layer_scratch_bytes",
+           "fa_layer_attend", "fa_layer_decode_path"]
 
 i32, i64, vp, f32, sz = C.c_int32, C.c_int64, C.c_void_p, C.c_float, C.c_size_t
 
@@ -42,6 +44,24 @@ class DecodeArgs(C.Structure):
         ("out", vp), ("m_out", vp), ("l_out", vp),
         ("scratch", vp), ("scratch_bytes", sz),
         ("phase_events_host", vp),
+        ("kn_h_host", vp), ("vn_h_host", vp),
+    ]
+
+
+class LayerDesc(C.Structure):
+    """Mirror of ``fa_layer_desc_t``."""
+    _fields_ = [
+        ("B", i32), ("Hkv", i32), ("D", i32), ("S", i32), ("W", i32), ("N", i32), ("T", i32), ("T_c", i32),
+        ("angle_mode", i32), ("dtype", i32), ("mid_l0", i32),
+        ("Mc_k", i32), ("Mn_k", i32), ("Mc_v", i32), ("Mn_v", i32),
+        ("with_il", i32),
+        ("kbuf", vp), ("vbuf", vp), ("buf_sb", i64), ("buf_rows", i32),
+        ("k_unc", vp), ("v_unc", vp), ("k_unc_sb", i64), ("v_unc_sb", i64), ("k_unc_sk", i64), ("v_unc_sk", i64),
+        ("unc_rows", i32),
+        ("k_coef", vp), ("v_coef", vp),
+        ("avg_k_u", vp), ("avg_k_d", vp), ("scale_k", vp), ("avg_v_u", vp), ("avg_v_d", vp), ("scale_v", vp),
+        ("kc_list", vp), ("kc_h", vp), ("kn_list", vp), ("kn_h", vp),
+        ("vc_list", vp), ("vc_h", vp), ("vn_list", vp), ("vn_h", vp),
         ("kn_h_host", vp), ("vn_h_host", vp),
     ]
 
@@ -81,6 +101,15 @@ def _load():
     lib.fa_decode_attn.argtypes = [C.POINTER(DecodeArgs), vp]
     lib.fa_decode_attn_static.argtypes = [C.POINTER(DecodeArgs), vp]
     lib.fa_merge.argtypes = [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp, vp]
+    lib.fa_layer_create.argtypes = [C.POINTER(LayerDesc), C.POINTER(vp)]
+    lib.fa_layer_destroy.argtypes = [vp]
+    lib.fa_layer_destroy.restype = None
+    lib.fa_layer_rebind_stores.argtypes = [vp, vp, vp, i64, i64, i64, i64, i32]
+    lib.fa_layer_update.argtypes = [vp, i32, i32, i64, i32, vp, vp, i64, i64, vp]
+    lib.fa_layer_scratch_bytes.argtypes = [vp, i32, i32]
+    lib.fa_layer_scratch_bytes.restype = sz
+    lib.fa_layer_attend.argtypes = [vp, i32, i32, i32, vp, i64, f32, vp, vp, vp, vp, sz, vp, vp]
+    lib.fa_layer_decode_path.argtypes = [vp]
     for name in EXPORTS:
         f = getattr(lib, name)
         if f.restype is C.c_int and name != "fa_version":

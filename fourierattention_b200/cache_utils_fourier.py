@@ -235,12 +235,14 @@ class DynamicCache(Cache):
         last_rank = self.seq_shard is None or self.seq_shard[0] == self.seq_shard[1] - 1
         cap = (r1 - r0) + (self.maxnewtokens + 8 if last_rank else 0)
         Mn_k, Mn_v = tb.kn_list.numel(), tb.vn_list.numel()
-        st.kbuf = torch.empty((B, S + 2 * W, F), dtype=dtype, device=dev)
-        st.vbuf = torch.empty((B, S + 2 * W, F), dtype=dtype, device=dev)
+        # zero-filled: the kernels fetch whole tiles, and rows a tile covers beyond the live ones (masked with
+        # probability 0) must hold finite values
+        st.kbuf = torch.zeros((B, S + 2 * W, F), dtype=dtype, device=dev)
+        st.vbuf = torch.zeros((B, S + 2 * W, F), dtype=dtype, device=dev)
         st.kbuf[:, :S].copy_(key_states[:, :S]); st.kbuf[:, S:S + W].copy_(key_states[:, P - W:])
         st.vbuf[:, :S].copy_(value_states[:, :S]); st.vbuf[:, S:S + W].copy_(value_states[:, P - W:])
-        st.k_unc = torch.empty((B, max(cap, 1), max(_round8(Mn_k), 8)), dtype=dtype, device=dev)
-        st.v_unc = torch.empty((B, max(cap, 1), max(_round8(Mn_v), 8)), dtype=dtype, device=dev)
+        st.k_unc = torch.zeros((B, max(cap, 1), max(_round8(Mn_k), 8)), dtype=dtype, device=dev)
+        st.v_unc = torch.zeros((B, max(cap, 1), max(_round8(Mn_v), 8)), dtype=dtype, device=dev)
         st.n_mid = r1 - r0
         k_coef, k_ua, k_ia, k_idev, k_udev = self._compress_side(key_states, S, P - W, tb.kc_list, tb.kn_list,
                                                                   st.k_unc[:, :st.n_mid, :Mn_k], dtype)
@@ -340,8 +342,12 @@ class DynamicCache(Cache):
         if q_len != 1:
             raise ValueError("decode updates carry one token")
         # The reference's branch test reads the batch size where the window length was meant
-        # (cache_utils_fourier.py:680); after a compressed prefill it reaches the eviction branch iff
-        # n_mid + B + 1 > W, which holds for every practical configuration.
+        # (cache_utils_fourier.py:680): with q_len = S + M + n_mid + B + 1 it appends to the window while
+        # q_len <= maxlen (n_mid + B + 1 <= W), re-compresses when q_len == maxlen + 1 (n_mid + B == W) and
+        # evicts otherwise.  Every practical configuration has n_mid + B > W and evicts.  At the boundary
+        # n_mid + B == W the reference's re-compression appends a second cache entry for the layer and its
+        # state is unusable afterwards; this cache evicts there too (the behaviour on either side of it),
+        # and only the window-growth case below it is refused.
         n_mid_total = self.curr_tokennum[layer_idx]
         if n_mid_total + bsz + 1 <= self.maxlocallen:
             raise NotImplementedError("window growth after a compressed prefill (cache_utils_fourier.py:681-729) "
@@ -351,7 +357,7 @@ class DynamicCache(Cache):
         phase = self.curr_tokennum[layer_idx]
         appends = self.seq_shard is None or self.seq_shard[0] == self.seq_shard[1] - 1   # else another rank stores the row
         if appends and st.n_mid + 1 > st.k_unc.shape[1]:
-            grow = lambda b: torch.cat([b, torch.empty_like(b)], dim=1)
+            grow = lambda b: torch.cat([b, torch.zeros_like(b)], dim=1)
             st.k_unc, st.v_unc = grow(st.k_unc), grow(st.v_unc)
             st.calls.rebind(st.k_unc, st.v_unc)
         # eviction into the coefficients, verbatim append and window slide in one launch
@@ -384,7 +390,7 @@ class DynamicCache(Cache):
             out = st.calls.attend(q, st.off, st.n_mid, num_head_q, sm_scale, phase_events)
             return out.view(B, num_head_q, 1, D)
         import torch.distributed as dist
-        out, m, l = st.calls.attend(q, st.off, st.n_mid, num_head_q, sm_scale, return_lse=True)
+        out, m, l = self.partial_attention(q, layer_idx, num_head_q, sm_scale)
         world = self.seq_shard[1]
         rows = B * num_head_q
         pack = torch.cat([out.view(rows, D), m.view(rows, 1), l.view(rows, 1)], dim=1)
@@ -392,6 +398,23 @@ class DynamicCache(Cache):
         dist.all_gather_into_tensor(gathered, pack, group=self.process_group)
         merged = ops.merge(gathered[:, :, :D], gathered[:, :, D], gathered[:, :, D + 1])
         return merged.view(B, num_head_q, 1, D)
+
+    def set_layer_statistics(self, layer_idx: int, stats32):
+        """Make the attention kernels of ``layer_idx`` use these float32 statistics ``(k_layer_average,
+        kd_layer_average, k_scale, v_layer_average, vd_layer_average, v_scale)``, each ``(B, Mc)`` (for
+        instance statistics restored from a saved cache); the public per-layer lists are not touched."""
+        st = self._state[layer_idx]
+        st.stats32 = tuple(t.to(torch.float32).contiguous() for t in stats32)
+        st.calls.set_statistics(st.stats32)
+
+    def partial_attention(self, query, layer_idx: int, num_head_q: int, sm_scale: float = -1.0):
+        """This rank's share of the attention under a sequence split: the output normalised over the keys the
+        rank holds, ``(B, Hq, D)``, with the softmax statistics ``(m, l)``, each ``(B, Hq)`` (maximum score in
+        the log2 domain, denominator relative to it), that the log-sum-exp merge needs
+        (fourier_triton_valid4_v2.py:756-776).  A rank without any key returns ``l = 0``."""
+        st = self._state[layer_idx]
+        q = query if query.dim() == 2 else query[:, 0]
+        return st.calls.attend(q, st.off, st.n_mid, num_head_q, sm_scale, return_lse=True)
 
     # ------------------------------------------------------------------------------------------
     def get_seq_length(self, layer_idx: Optional[int] = 0) -> int:

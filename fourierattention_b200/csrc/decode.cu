@@ -8,17 +8,19 @@
 // J consecutive tokens is a fixed J x N table times a per-frequency rotation, so the table lives in
 // shared memory for the whole kernel and only w (forward) and g (backward) are rotated per tile.
 //
-// Four launches per call:
+// Three launches per call:
 //   prepare  : w and const from q and C_k                      (reads C_k once)
 //   main     : split-KV pass over sinks+window rows and over the middle span; per chunk partials
 //              (max, denominator, verbatim-V numerator, g)      (reads every cache row once)
-//   contract : merge g over chunks, contract with C_v           (reads C_v once)
-//   output   : merge numerators/denominators, add the compressed-V part, normalise
+//   finish   : merge g over chunks and contract it with C_v (reads C_v once), merge numerators and
+//              denominators, add the compressed-V part, normalise
 #include <cuda.h>
 #include <math.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include <mutex>
+#include <new>
 #include <type_traits>
 
 #include "common.cuh"
@@ -45,6 +47,7 @@ struct DecodeParams {
   fa_decode_args_t a;
   int R, F, n_il;
   int TRm, il_tpc;  // tensor-core sinks+window pass: rows per tile, tiles per chunk
+  int sink_row0, win_row0;  // row of the sink / window tensor maps where the first sink / window row lies
   float c2;  // sm_scale * log2(e)
   // plan
   int J, kvh, HG, HGp, n_groups, TR, Hqp;
@@ -716,27 +719,17 @@ template <typename T, int NT, int NH>
 __global__ void __launch_bounds__(FAST_THREADS, 1) decode_main_fast_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int b = blockIdx.y;
-#ifdef FA_PHASE_TIMING
-  const long long cta_t0 = clock64();
-#endif
   if ((int)blockIdx.x < p.n_il_chunks) {
     il_chunk_mma<T>(p, b, blockIdx.x, smem_raw);
   } else {
     mid_chunk_fast<T, NT, NH>(p, b, blockIdx.x - p.n_il_chunks, smem_raw);
   }
-#ifdef FA_PHASE_TIMING
-  if (threadIdx.x == 0)
-    atomicAdd(&g_phase_clk[(int)blockIdx.x < p.n_il_chunks ? 14 : 15], (unsigned long long)(clock64() - cta_t0));
-#endif
 }
 
 template <typename T>
 __global__ void __launch_bounds__(WS_T, 1) decode_main_ws_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int b = blockIdx.y;
-#ifdef FA_PHASE_TIMING
-  const long long cta_t0 = clock64();
-#endif
   // blockIdx.y is a group of wsSEQ sequences: first the sinks+window CTAs of each of them, then the group's
   // middle-span CTAs
   const int n_il_ctas = p.wsSEQ * p.n_il_chunks;
@@ -744,14 +737,8 @@ __global__ void __launch_bounds__(WS_T, 1) decode_main_ws_kernel(const __grid_co
     const int seq = blockIdx.x / p.n_il_chunks, chunk = blockIdx.x - seq * p.n_il_chunks;
     if (b * p.wsSEQ + seq >= p.a.B) return;
     il_chunk_mma<T>(p, b * p.wsSEQ + seq, chunk, smem_raw);
-#ifdef FA_PHASE_TIMING
-    if (threadIdx.x == 0) atomicAdd(&g_phase_clk[14], (unsigned long long)(clock64() - cta_t0));
-#endif
   } else {
     mid_chunk_ws<T>(p, b * p.wsSEQ, blockIdx.x - n_il_ctas, smem_raw);
-#ifdef FA_PHASE_TIMING
-    if (threadIdx.x == 256) atomicAdd(&g_phase_clk[15], (unsigned long long)(clock64() - cta_t0));
-#endif
   }
 }
 
@@ -952,7 +939,38 @@ __global__ void merge_kernel(const float* __restrict__ o, const float* __restric
 // ---------------------------------------------------------------------------------------------
 constexpr int SMEM_LIMIT = 200 * 1024;
 
-static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
+// Switches of the planner.  The one-shot entry points read them from the environment on every call (FA_DECODE_EXACT,
+// FA_DECODE_NO_WS); a layer handle reads them once when it is created.
+struct PlanFlags {
+  bool force_exact, no_ws;
+};
+static PlanFlags env_flags() {
+  PlanFlags f;
+  f.force_exact = getenv("FA_DECODE_EXACT") != nullptr;
+  f.no_ws = getenv("FA_DECODE_NO_WS") != nullptr;
+  return f;
+}
+
+// scratch layout (floats, each block 16-byte aligned); depends on the plan's chunk counts only
+static void bind_scratch(DecodeParams& p, void* scratch) {
+  const fa_decode_args_t& a = p.a;
+  int64_t o = 0;
+  auto take = [&](int64_t n) {
+    int64_t r = o;
+    o += (n + 3) / 4 * 4;
+    return r;
+  };
+  const int64_t B = a.B, Hq = a.Hq;
+  const int64_t ow = take(B * Hq * 2 * a.N), oc = take(B * Hq), om = take(B * p.NCH * Hq), ol = take(B * p.NCH * Hq);
+  const int64_t oo = take(B * p.NCH * Hq * a.D), og = take(B * p.n_mid_chunks * Hq * 2 * a.N);
+  const int64_t oe = take(4);
+  p.scratch_floats = o;
+  float* s = reinterpret_cast<float*>(scratch);
+  p.w = s + ow; p.cst = s + oc; p.m_part = s + om; p.l_part = s + ol; p.o_part = s + oo; p.g_part = s + og;
+  p.err = reinterpret_cast<int*>(s + oe);
+}
+
+static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags& flags) {
   FA_REQUIRE(a.B > 0 && a.Hq > 0 && a.Hkv > 0 && a.D > 0, FA_ERR_SHAPE, "fa_decode_attn: B, Hq, Hkv, D must be positive");
   FA_REQUIRE(a.Hq % a.Hkv == 0, FA_ERR_SHAPE, "fa_decode_attn: Hq (%d) must be a multiple of Hkv (%d)", a.Hq, a.Hkv);
   FA_REQUIRE(a.dtype == FA_DTYPE_F16 || a.dtype == FA_DTYPE_BF16, FA_ERR_DTYPE, "fa_decode_attn: bad dtype %d", a.dtype);
@@ -960,7 +978,9 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
              "fa_decode_attn: no keys to attend");
   FA_REQUIRE(a.D % 8 == 0, FA_ERR_ALIGN, "fa_decode_attn: head_dim (%d) must be a multiple of 8", a.D);
   p.a = a;
-  p.force_exact = (getenv("FA_DECODE_EXACT") != nullptr);
+  p.force_exact = flags.force_exact;
+  p.sink_row0 = 0;
+  p.win_row0 = 0;
   p.R = a.Hq / a.Hkv;
   FA_REQUIRE(p.R <= R_MAX, FA_ERR_CAPACITY, "fa_decode_attn: at most %d query heads per KV head (got %d)", R_MAX, p.R);
   p.F = a.Hkv * a.D;
@@ -1046,7 +1066,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
       // warp-specialised form: 128-token super-tiles, and every 8-head column tile must find its
       // verbatim columns inside WS_KS (K) and WS_MTV (V) 16-column tiles, which only the host copies
       // of the offset tables can tell
-      if (p.fast && NH == 2 && a.kn_h_host && a.vn_h_host && getenv("FA_DECODE_NO_WS") == nullptr) {
+      if (p.fast && NH == 2 && a.kn_h_host && a.vn_h_host && !flags.no_ws) {
         bool ok = true;
         for (int nt = 0; nt < NT && ok; ++nt) {
           const int g0 = (8 * nt) / p.R, last = (a.Hq < 8 * nt + 8 ? a.Hq : 8 * nt + 8) - 1, g1 = last / p.R;
@@ -1072,7 +1092,11 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
       }
     }
     const int sms = sm_count();
-    const int max_chunks = ceil_div(a.n_mid, J);
+    // The split is made for the span length rounded up to whole super-tiles, so that the plan (chunk length,
+    // chunk count, scratch need) stays the same while n_mid grows inside one super-tile; every chunk still
+    // starts below n_mid.
+    const int n_mid_r = rup(a.n_mid, J);
+    const int max_chunks = n_mid_r / J;
     if (p.fast && p.n_il > 0) {
       // One wave of CTAs per launch.  Split the CTAs of a sequence between sinks+window rows and the
       // middle span so that the slowest CTA is as short as possible; costs in clock ticks as measured
@@ -1091,7 +1115,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
         int n_mid = per_seq - seqs * ceil_div(n_tiles, tpc);
         if (n_mid < 1) break;
         if (n_mid > max_chunks) n_mid = max_chunks;
-        const int mid_tok = rup(ceil_div(a.n_mid, n_mid), J);
+        const int mid_tok = rup(ceil_div(n_mid_r, n_mid), J);
         const double t_il = 8000.0 + cost_il_tile * tpc, t_mid = 24000.0 + cost_mid_tok * mid_tok;
         const double t = t_il > t_mid ? t_il : t_mid;
         if (t < best) {
@@ -1107,8 +1131,8 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
     if (p.fast == 2) target = sms / ceil_div(a.B, p.wsSEQ) - p.wsSEQ * p.n_il_chunks;
     if (target < 1) target = 1;
     if (target > max_chunks) target = max_chunks;
-    p.mid_chunk = rup(ceil_div(a.n_mid, target), J);
-    p.n_mid_chunks = ceil_div(a.n_mid, p.mid_chunk);
+    p.mid_chunk = rup(ceil_div(n_mid_r, target), J);
+    p.n_mid_chunks = ceil_div(n_mid_r, p.mid_chunk);
   }
   p.NCH = p.n_il_chunks + p.n_mid_chunks;
   const int il_need = p.fast ? il_smem_fast : il_smem;   // the 512-thread kernels run the sinks+window rows as MMAs
@@ -1116,30 +1140,35 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p) {
   if (p.n_il == 0) p.smem_main = mid_smem_bytes;
   FA_REQUIRE(p.smem_main <= 227 * 1024, FA_ERR_CAPACITY, "fa_decode_attn: shared memory need %d exceeds 227 KB", p.smem_main);
   p.smem_prepare = p.R * (a.D + 8) * 4;   // one KV head's column segment (at most D wide) plus alignment pads
-  // scratch layout (floats, each block 16-byte aligned)
-  int64_t o = 0;
-  auto take = [&](int64_t n) {
-    int64_t r = o;
-    o += (n + 3) / 4 * 4;
-    return r;
-  };
-  const int64_t B = a.B, Hq = a.Hq;
-  const int64_t ow = take(B * Hq * 2 * a.N), oc = take(B * Hq), om = take(B * p.NCH * Hq), ol = take(B * p.NCH * Hq);
-  const int64_t oo = take(B * p.NCH * Hq * a.D), og = take(B * p.n_mid_chunks * Hq * 2 * a.N);
-  const int64_t oe = take(4);
-  p.scratch_floats = o;
-  float* s = reinterpret_cast<float*>(a.scratch);
-  p.w = s + ow; p.cst = s + oc; p.m_part = s + om; p.l_part = s + ol; p.o_part = s + oo; p.g_part = s + og;
-  p.err = reinterpret_cast<int*>(s + oe);
+  bind_scratch(p, a.scratch);
   return FA_OK;
 }
 
+// Raises a kernel's dynamic shared-memory limit; remembers per (device, kernel) what has been granted, so the
+// attribute call is made once and not on every launch.
 template <typename K>
 static int set_smem(K kernel, int bytes) {
-  if (bytes > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
-  }
+  if (bytes <= 48 * 1024) return FA_OK;
+  struct Entry {
+    int dev;
+    const void* fn;
+    int bytes;
+  };
+  static std::mutex mu;
+  static Entry seen[256];
+  static int n_seen = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const void* fn = reinterpret_cast<const void*>(kernel);
+  std::lock_guard<std::mutex> lock(mu);
+  Entry* hit = nullptr;
+  for (int i = 0; i < n_seen; ++i)
+    if (seen[i].dev == dev && seen[i].fn == fn) hit = &seen[i];
+  if (hit && hit->bytes >= bytes) return FA_OK;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
+  if (hit) hit->bytes = bytes;
+  else if (n_seen < 256) seen[n_seen++] = Entry{dev, fn, bytes};
   return FA_OK;
 }
 
@@ -1225,7 +1254,7 @@ extern "C" size_t fa_decode_scratch_bytes(const fa_decode_args_t* args) {
   DecodeParams p;
   fa_decode_args_t a = *args;
   a.scratch = nullptr;
-  if (make_plan(a, p) != FA_OK) return 0;
+  if (make_plan(a, p, env_flags()) != FA_OK) return 0;
   return (size_t)p.scratch_floats * sizeof(float);
 }
 
@@ -1234,17 +1263,14 @@ extern "C" int fa_decode_path(const fa_decode_args_t* args) {
   DecodeParams p;
   fa_decode_args_t a = *args;
   a.scratch = nullptr;
-  int rc = make_plan(a, p);
+  int rc = make_plan(a, p, env_flags());
   if (rc != FA_OK) return rc;
   return a.n_mid > 0 ? p.fast : 0;
 }
 
-extern "C" int fa_decode_attn(const fa_decode_args_t* args, fa_stream_t stream) {
-  FA_REQUIRE(args, FA_ERR_NULL, "fa_decode_attn: null argument block");
-  const fa_decode_args_t& a = *args;
-  DecodeParams p;
-  int rc = make_plan(a, p);
-  if (rc != FA_OK) return rc;
+// Pointer / alignment checks of a planned call (p.a holds the caller's arguments, scratch already bound).
+static int validate_planned(const DecodeParams& p) {
+  const fa_decode_args_t& a = p.a;
   FA_REQUIRE(a.q && a.out, FA_ERR_NULL, "fa_decode_attn: q / out is null");
   FA_REQUIRE(a.n_sink == 0 || (a.k_sink && a.v_sink), FA_ERR_NULL, "fa_decode_attn: sink rows are null");
   FA_REQUIRE(a.n_win == 0 || (a.k_win && a.v_win), FA_ERR_NULL, "fa_decode_attn: window rows are null");
@@ -1271,6 +1297,14 @@ extern "C" int fa_decode_attn(const fa_decode_args_t* args, fa_stream_t stream) 
     FA_REQUIRE(al16(a.k_win) && al16(a.v_win) && a.win_sb % 8 == 0, FA_ERR_ALIGN,
                "fa_decode_attn: window rows must be 16-byte aligned");
   FA_REQUIRE(a.q_sb % 8 == 0 || a.B == 1, FA_ERR_ALIGN, "fa_decode_attn: q batch stride must be a multiple of 8");
+  return FA_OK;
+}
+
+// One-shot form: tensor maps over exactly the rows of this call (rows past them read as zeros).
+static int decode_planned(DecodeParams& p, cudaStream_t st) {
+  const fa_decode_args_t& a = p.a;
+  int rc = validate_planned(p);
+  if (rc != FA_OK) return rc;
   if (p.fast) {
     if (a.n_sink > 0 &&
         ((rc = make_tensor_map_3d(&p.tm_ks, a.k_sink, a.dtype, p.F, a.n_sink, p.F, a.B, a.sink_sb, 64, p.TRm)) != FA_OK ||
@@ -1285,8 +1319,15 @@ extern "C" int fa_decode_attn(const fa_decode_args_t* args, fa_stream_t stream) 
     if (a.Mn_v > 0 && (rc = make_tensor_map_3d(&p.tm_v, a.v_mn, a.dtype, a.Mn_v, a.n_mid, a.v_mn_sk, a.B, a.v_mn_sb, 64, 64)) != FA_OK)
       return rc;
   }
-  cudaStream_t st = (cudaStream_t)stream;
   return a.dtype == FA_DTYPE_F16 ? launch_decode<__half>(p, st) : launch_decode<__nv_bfloat16>(p, st);
+}
+
+extern "C" int fa_decode_attn(const fa_decode_args_t* args, fa_stream_t stream) {
+  FA_REQUIRE(args, FA_ERR_NULL, "fa_decode_attn: null argument block");
+  DecodeParams p;
+  int rc = make_plan(*args, p, env_flags());
+  if (rc != FA_OK) return rc;
+  return decode_planned(p, (cudaStream_t)stream);
 }
 
 extern "C" int fa_merge(const float* o, const float* m, const float* l, int n_parts, int rows, int D, float* out,
@@ -1304,7 +1345,7 @@ extern "C" int fa_decode_attn_static(const fa_decode_args_t* args, fa_stream_t s
   a.scratch = nullptr;
   a.scratch_bytes = 0;
   DecodeParams p;
-  int rc = make_plan(a, p);
+  int rc = make_plan(a, p, env_flags());
   if (rc != FA_OK) return rc;
   const size_t need = (size_t)p.scratch_floats * sizeof(float);
   FA_REQUIRE(need <= (size_t)FA_DECODE_STATIC_SCRATCH_BYTES, FA_ERR_CAPACITY,
@@ -1313,21 +1354,186 @@ extern "C" int fa_decode_attn_static(const fa_decode_args_t* args, fa_stream_t s
   void* ptr = nullptr;
   rc = static_scratch_address(&ptr);
   if (rc != FA_OK) return rc;
-  a.scratch = ptr;
-  a.scratch_bytes = (size_t)FA_DECODE_STATIC_SCRATCH_BYTES;
-  return fa_decode_attn(&a, stream);
+  p.a.scratch = ptr;
+  p.a.scratch_bytes = (size_t)FA_DECODE_STATIC_SCRATCH_BYTES;
+  bind_scratch(p, ptr);   // the plan made above stands; only the scratch pointers move
+  return decode_planned(p, (cudaStream_t)stream);
 }
 
-#ifdef FA_PHASE_TIMING
-// debugging aid (only in builds with -DFA_PHASE_TIMING): cumulative clock ticks per phase of the
-// tensor-core middle-span pass, thread 0 of every CTA
-extern "C" int fa_debug_phase_clocks(unsigned long long* out16_host, int reset) {
-  cudaDeviceSynchronize();
-  if (out16_host) cudaMemcpyFromSymbol(out16_host, fa::g_phase_clk, sizeof(unsigned long long) * 16);
-  if (reset) {
-    unsigned long long z[16] = {0};
-    cudaMemcpyToSymbol(fa::g_phase_clk, z, sizeof(z));
-  }
-  return 0;
+
+// ---------------------------------------------------------------------------------------------
+// Layer handle: everything of one cached layer that does not change between decode steps is bound once
+// (buffers, tables, statistics, planner switches, tensor maps over the WHOLE allocations), so a decode
+// step costs two short calls on the host.  The window slides inside its buffer and the middle span
+// grows by a row per step; both enter as plain integers (window offset, n_mid): the window's position is
+// a row coordinate of the tensor-copy requests, n_mid bounds the tokens a chunk walks.  The plan is kept
+// while n_mid stays inside one super-tile and the query-head count does not change.
+// ---------------------------------------------------------------------------------------------
+struct fa_layer {
+  fa_layer_desc_t d;
+  PlanFlags flags;
+  DecodeParams p;
+  bool planned, maps_ready;
+  int plan_lo, plan_hi, plan_Hq, plan_TRm, plan_fast;
+  int last_path;
+};
+
+extern "C" int fa_layer_create(const fa_layer_desc_t* desc, fa_layer_t** out) {
+  FA_REQUIRE(desc && out, FA_ERR_NULL, "fa_layer_create: null argument");
+  const fa_layer_desc_t& d = *desc;
+  FA_REQUIRE(d.B > 0 && d.Hkv > 0 && d.D > 0 && d.S >= 0 && d.W > 0 && d.N > 0 && d.T > 0 && d.T_c > 0, FA_ERR_SHAPE,
+             "fa_layer_create: sizes must be positive");
+  FA_REQUIRE(d.dtype == FA_DTYPE_F16 || d.dtype == FA_DTYPE_BF16, FA_ERR_DTYPE, "fa_layer_create: bad dtype %d", d.dtype);
+  FA_REQUIRE(d.kbuf && d.vbuf && d.buf_rows >= d.S + 2 * d.W, FA_ERR_SHAPE,
+             "fa_layer_create: the window buffers must hold S + 2W rows");
+  FA_REQUIRE(d.unc_rows > 0 && (d.Mn_k == 0 || d.k_unc) && (d.Mn_v == 0 || d.v_unc), FA_ERR_NULL,
+             "fa_layer_create: verbatim store missing");
+  FA_REQUIRE(d.Mc_k + d.Mn_k == d.Hkv * d.D && d.Mc_v + d.Mn_v == d.Hkv * d.D, FA_ERR_SHAPE,
+             "fa_layer_create: compressed + verbatim dims must add up to Hkv*D");
+  fa_layer* L = new (std::nothrow) fa_layer();
+  FA_REQUIRE(L != nullptr, FA_ERR_CAPACITY, "fa_layer_create: out of host memory");
+  L->d = d;
+  L->flags = env_flags();
+  L->planned = false;
+  L->maps_ready = false;
+  L->last_path = 0;
+  *out = L;
+  return FA_OK;
 }
-#endif
+
+extern "C" void fa_layer_destroy(fa_layer_t* layer) { delete layer; }
+
+extern "C" int fa_layer_rebind_stores(fa_layer_t* L, void* k_unc, void* v_unc, int64_t k_unc_sb, int64_t v_unc_sb,
+                                      int64_t k_unc_sk, int64_t v_unc_sk, int32_t unc_rows) {
+  FA_REQUIRE(L, FA_ERR_NULL, "fa_layer_rebind_stores: null handle");
+  L->d.k_unc = k_unc; L->d.v_unc = v_unc;
+  L->d.k_unc_sb = k_unc_sb; L->d.v_unc_sb = v_unc_sb; L->d.k_unc_sk = k_unc_sk; L->d.v_unc_sk = v_unc_sk;
+  L->d.unc_rows = unc_rows;
+  L->planned = false;
+  L->maps_ready = false;
+  return FA_OK;
+}
+
+extern "C" int fa_layer_update(fa_layer_t* L, int32_t win_off, int32_t n_mid, int64_t phase, int32_t appends,
+                               const void* k_new, const void* v_new, int64_t new_sb, int64_t new_sh,
+                               fa_stream_t stream) {
+  FA_REQUIRE(L, FA_ERR_NULL, "fa_layer_update: null handle");
+  const fa_layer_desc_t& d = L->d;
+  FA_REQUIRE(win_off >= 0 && win_off < d.W && n_mid >= 0, FA_ERR_SHAPE, "fa_layer_update: bad window offset or n_mid");
+  FA_REQUIRE(!appends || n_mid < d.unc_rows, FA_ERR_CAPACITY, "fa_layer_update: the verbatim stores are full (%d rows)",
+             d.unc_rows);
+  const int64_t F = (int64_t)d.Hkv * d.D, es = 2;
+  unsigned char* kb = reinterpret_cast<unsigned char*>(d.kbuf);
+  unsigned char* vb = reinterpret_cast<unsigned char*>(d.vbuf);
+  const int64_t row_b = (int64_t)(d.S + win_off) * F * es, dst_b = row_b + (int64_t)d.W * F * es;
+  const int mn_k = appends ? d.Mn_k : 0, mn_v = appends ? d.Mn_v : 0;
+  unsigned char* ku = reinterpret_cast<unsigned char*>(d.k_unc) + (int64_t)n_mid * d.k_unc_sk * es;
+  unsigned char* vu = reinterpret_cast<unsigned char*>(d.v_unc) + (int64_t)n_mid * d.v_unc_sk * es;
+  return fa_evict_step(d.Mc_k ? d.k_coef : nullptr, kb + row_b, d.buf_sb, d.kc_list, d.Mc_k,
+                       d.Mc_v ? d.v_coef : nullptr, vb + row_b, d.buf_sb, d.vc_list, d.Mc_v, d.N, phase, d.T_c,
+                       d.angle_mode, kb + row_b, vb + row_b, d.buf_sb, d.kn_list, mn_k, d.vn_list, mn_v, ku, d.k_unc_sb,
+                       vu, d.v_unc_sb, k_new, v_new, new_sb, new_sh, kb + dst_b, vb + dst_b, d.buf_sb, d.dtype, d.B,
+                       d.Hkv, d.D, stream);
+}
+
+// (re)plans for the query-head count and the super-tile n_mid lies in
+static int layer_plan(fa_layer* L, int Hq, int n_mid, float sm_scale) {
+  const fa_layer_desc_t& d = L->d;
+  fa_decode_args_t a;
+  memset(&a, 0, sizeof(a));
+  a.B = d.B; a.Hq = Hq; a.Hkv = d.Hkv; a.D = d.D;
+  a.n_sink = d.with_il ? d.S : 0;
+  a.n_win = d.with_il ? d.W : 0;
+  a.n_mid = n_mid; a.mid_l0 = d.mid_l0; a.N = d.N; a.T = d.T;
+  a.Mc_k = d.Mc_k; a.Mn_k = d.Mn_k; a.Mc_v = d.Mc_v; a.Mn_v = d.Mn_v;
+  a.dtype = d.dtype; a.sm_scale = sm_scale;
+  a.k_sink = d.kbuf; a.v_sink = d.vbuf; a.sink_sb = d.buf_sb;
+  a.k_win = d.kbuf; a.v_win = d.vbuf; a.win_sb = d.buf_sb;
+  a.k_mn = d.k_unc; a.v_mn = d.v_unc; a.k_mn_sb = d.k_unc_sb; a.v_mn_sb = d.v_unc_sb;
+  a.k_mn_sk = d.k_unc_sk; a.v_mn_sk = d.v_unc_sk;
+  a.k_coef = d.k_coef; a.v_coef = d.v_coef;
+  a.avg_k_u = d.avg_k_u; a.avg_k_d = d.avg_k_d; a.scale_k = d.scale_k;
+  a.avg_v_u = d.avg_v_u; a.avg_v_d = d.avg_v_d; a.scale_v = d.scale_v;
+  a.kc_list = d.kc_list; a.kc_h = d.kc_h; a.kn_list = d.kn_list; a.kn_h = d.kn_h;
+  a.vc_list = d.vc_list; a.vc_h = d.vc_h; a.vn_list = d.vn_list; a.vn_h = d.vn_h;
+  a.kn_h_host = d.kn_h_host; a.vn_h_host = d.vn_h_host;
+  int rc = make_plan(a, L->p, L->flags);
+  if (rc != FA_OK) return rc;
+  DecodeParams& p = L->p;
+  L->planned = true;
+  L->plan_Hq = Hq;
+  L->plan_hi = n_mid > 0 ? rup(n_mid, p.J) : 0;
+  L->plan_lo = n_mid > 0 ? L->plan_hi - p.J : -1;
+  L->last_path = n_mid > 0 ? p.fast : 0;
+  return FA_OK;
+}
+
+// tensor maps, one per buffer, over every row it owns: sinks at rows [0, S), the window wherever it has slid to;
+// encoded once (again only if the stores are rebound or the tile height of the sinks+window pass changes)
+static int layer_maps(fa_layer* L) {
+  const fa_layer_desc_t& d = L->d;
+  DecodeParams& p = L->p;
+  if (!p.fast || (L->maps_ready && L->plan_TRm == p.TRm)) return FA_OK;
+  int rc;
+  if (d.with_il) {
+    if ((rc = make_tensor_map_3d(&p.tm_ks, d.kbuf, d.dtype, p.F, d.buf_rows, p.F, d.B, d.buf_sb, 64, p.TRm)) != FA_OK ||
+        (rc = make_tensor_map_3d(&p.tm_vs, d.vbuf, d.dtype, p.F, d.buf_rows, p.F, d.B, d.buf_sb, 64, p.TRm)) != FA_OK)
+      return rc;
+    p.tm_kw = p.tm_ks;
+    p.tm_vw = p.tm_vs;
+  }
+  if (d.Mn_k > 0 && (rc = make_tensor_map_3d(&p.tm_k, d.k_unc, d.dtype, d.Mn_k, d.unc_rows, d.k_unc_sk, d.B, d.k_unc_sb, 64, 64)) != FA_OK)
+    return rc;
+  if (d.Mn_v > 0 && (rc = make_tensor_map_3d(&p.tm_v, d.v_unc, d.dtype, d.Mn_v, d.unc_rows, d.v_unc_sk, d.B, d.v_unc_sb, 64, 64)) != FA_OK)
+    return rc;
+  L->maps_ready = true;
+  L->plan_TRm = p.TRm;
+  return FA_OK;
+}
+
+static bool layer_plan_holds(const fa_layer* L, int Hq, int n_mid) {
+  if (!L->planned || Hq != L->plan_Hq) return false;
+  if (n_mid == 0) return L->plan_hi == 0;
+  return n_mid > L->plan_lo && n_mid <= L->plan_hi;
+}
+
+extern "C" size_t fa_layer_scratch_bytes(fa_layer_t* L, int32_t Hq, int32_t n_mid) {
+  if (!L) return 0;
+  if (!layer_plan_holds(L, Hq, n_mid) && layer_plan(L, Hq, n_mid, -1.0f) != FA_OK) return 0;
+  return (size_t)L->p.scratch_floats * sizeof(float);
+}
+
+extern "C" int fa_layer_decode_path(fa_layer_t* L) { return L ? L->last_path : FA_ERR_NULL; }
+
+extern "C" int fa_layer_attend(fa_layer_t* L, int32_t win_off, int32_t n_mid, int32_t Hq, const void* q, int64_t q_sb,
+                               float sm_scale, float* out, float* m_out, float* l_out, void* scratch,
+                               size_t scratch_bytes, void* const* phase_events_host, fa_stream_t stream) {
+  FA_REQUIRE(L, FA_ERR_NULL, "fa_layer_attend: null handle");
+  const fa_layer_desc_t& d = L->d;
+  FA_REQUIRE(win_off >= 0 && win_off <= d.W && n_mid >= 0 && n_mid <= d.unc_rows, FA_ERR_SHAPE,
+             "fa_layer_attend: bad window offset or n_mid");
+  int rc;
+  if (!layer_plan_holds(L, Hq, n_mid) && (rc = layer_plan(L, Hq, n_mid, sm_scale)) != FA_OK) return rc;
+  if ((rc = layer_maps(L)) != FA_OK) return rc;
+  DecodeParams& p = L->p;
+  fa_decode_args_t& a = p.a;
+  const int64_t F = (int64_t)d.Hkv * d.D;
+  a.n_mid = n_mid;
+  a.q = q; a.q_sb = q_sb;
+  a.sm_scale = sm_scale;
+  const float sc = (sm_scale > 0.f) ? sm_scale : 1.0f / sqrtf((float)d.D);
+  p.c2 = sc * 1.4426950408889634f;
+  a.out = out; a.m_out = m_out; a.l_out = l_out;
+  a.phase_events_host = phase_events_host;
+  a.scratch = scratch; a.scratch_bytes = scratch_bytes;
+  bind_scratch(p, scratch);
+  if (d.with_il) {
+    a.k_win = reinterpret_cast<unsigned char*>(d.kbuf) + (int64_t)(d.S + win_off) * F * 2;
+    a.v_win = reinterpret_cast<unsigned char*>(d.vbuf) + (int64_t)(d.S + win_off) * F * 2;
+    p.sink_row0 = 0;
+    p.win_row0 = d.S + win_off;
+  }
+  if ((rc = validate_planned(p)) != FA_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  return d.dtype == FA_DTYPE_F16 ? launch_decode<__half>(p, st) : launch_decode<__nv_bfloat16>(p, st);
+}

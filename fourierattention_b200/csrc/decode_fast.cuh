@@ -24,19 +24,6 @@
 // fills with TMA tensor-map boxes (64 columns x 64 tokens, 128-byte swizzle) completing on mbarriers.
 #pragma once
 
-#ifdef FA_PHASE_TIMING
-__device__ unsigned long long g_phase_clk[16];
-#define FA_TICK(i)                                                     \
-  do {                                                                 \
-    if (tid == 0) {                                                    \
-      const long long now__ = clock64();                               \
-      atomicAdd(&g_phase_clk[i], (unsigned long long)(now__ - tick__)); \
-      tick__ = now__;                                                  \
-    }                                                                  \
-  } while (0)
-#else
-#define FA_TICK(i)
-#endif
 
 constexpr int FD = 16;   // interpolation nodes per super-tile
 constexpr int FH = 64;   // tokens per half tile (staging granularity)
@@ -269,9 +256,6 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
   const int halfN = N / 2;
   const int fk0 = tid / halfN, fp0 = tid % halfN, fdk = FAST_T / halfN, fdp = FAST_T % halfN;
 
-#ifdef FA_PHASE_TIMING
-  long long tick__ = clock64();
-#endif
   // ---- setup ------------------------------------------------------------------------------
   // The ring of half tiles is filled by the tensor-copy engine (TMA): lane 0 of warp 7 issues one copy
   // per 64 x 64 box and the bytes landing complete the slot's mbarrier.  A slot is refilled only after a CTA barrier that every
@@ -427,7 +411,6 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
   const int mt4 = wp & 3, ntp = wp >> 2;   // 16-token slice of a half tile, column-tile group
   consumer_sync();
 
-  FA_TICK(0);
   int mbuf = 0;            // which copy of m_run holds the current maxima
   int use_slot = 0;        // ring slot of the next half tile to consume
   uint32_t use_round = 0;  // how many times the ring has wrapped
@@ -466,7 +449,6 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
       }
     }
     consumer_sync();
-    FA_TICK(1);
     // ---- B: scores at the nodes,  s_node[16 x HN] = Fn_t[16 x 2N] * w[2N x HN] ------------------
     // warp = (column tile, half of the 2N rows); four accumulators keep the MMA chains short
     if (nt1 < NT) {
@@ -508,7 +490,6 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
     }
     consumer_sync();
 
-    FA_TICK(2);
     float pt_acc[4] = {0.f, 0.f, 0.f, 0.f};   // probabilities projected on the nodes (warps < NT)
 #pragma unroll 1
     for (int half = 0; half < NH; ++half) {
@@ -539,9 +520,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
         }
       }
       // ---- D: verbatim-dim scores from the K rows ----------------------------------------------
-      FA_TICK(3);
       mbar_wait(bars + use_slot, use_round & 1, dead, p.err);
-      FA_TICK(4);
       {
         const unsigned char* ks_ = reinterpret_cast<const unsigned char*>(slots) + use_slot * L.slot_bytes;
 #pragma unroll
@@ -570,7 +549,6 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
         use_slot = 0;
         ++use_round;
       }
-      FA_TICK(5);
       // ---- E: online softmax over the 64 tokens of this half -----------------------------------
       const bool ok0 = (tok0 + 16 * mt4 + gq) < l1, ok1 = (tok0 + 16 * mt4 + gq + 8) < l1;
 #pragma unroll
@@ -653,7 +631,6 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
       }
       mbuf ^= 1;
       consumer_sync();
-      FA_TICK(6);
       // ---- F: project the probabilities onto the nodes (warps 0..NT-1, one column tile each) -----
       if (wp < NT) {
         const int col = 8 * wp + 2 * tq;
@@ -671,9 +648,7 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
         }
       }
       // ---- G: verbatim-V numerators from the V rows ----------------------------------------------
-      FA_TICK(7);
       mbar_wait(bars + use_slot, use_round & 1, dead, p.err);
-      FA_TICK(8);
       {
         const unsigned char* vs_ = reinterpret_cast<const unsigned char*>(slots) + use_slot * L.slot_bytes;
 #pragma unroll
@@ -715,7 +690,6 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
         ++use_round;
       }
     }
-    FA_TICK(9);
     // ---- H: add the node-projected probabilities to g,  g[2N x HN] += Fn_t^T[2N x 16] * pt[16 x HN] ----
     if (wp < NT) {
       const int col = 8 * wp + 2 * tq;
@@ -761,7 +735,6 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
     }
     consumer_sync();
     for (int h = tid; h < HN; h += FAST_T) alpha_prod[h] = 1.f;
-    FA_TICK(10);
   }
   consumer_sync();
 
@@ -813,6 +786,3 @@ __device__ void mid_chunk_fast(const DecodeParams& p, int b, int chunk, unsigned
   }
 }
 
-#ifdef FA_PHASE_TIMING
-#undef FA_TICK
-#endif

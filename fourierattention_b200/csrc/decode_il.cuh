@@ -53,18 +53,6 @@ __device__ __forceinline__ int il_sw(int r, int chunk, int box_bytes) {
   return (chunk >> 3) * box_bytes + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
 }
 
-#ifdef FA_IL_TIMING
-#define IL_TICK(i)                                                      \
-  do {                                                                  \
-    if (threadIdx.x == 0) {                                             \
-      const long long now__ = clock64();                                \
-      atomicAdd(&g_phase_clk[i], (unsigned long long)(now__ - tick__)); \
-      tick__ = now__;                                                   \
-    }                                                                   \
-  } while (0)
-#else
-#define IL_TICK(i)
-#endif
 
 // scores + softmax of one KV head over all rows of a tile, by one warp (defined below)
 template <typename T>
@@ -109,7 +97,7 @@ __device__ void il_chunk_mma(const DecodeParams& p, int b, int chunk, unsigned c
     const int s = t % IL_STAGES;
     const int gt = t0 + t;
     const bool sink = gt < n_st;
-    const int row = (sink ? gt : gt - n_st) * TR;
+    const int row = (sink ? p.sink_row0 + gt * TR : p.win_row0 + (gt - n_st) * TR);
     const CUtensorMap* mk = sink ? &p.tm_ks : &p.tm_kw;
     const CUtensorMap* mv = sink ? &p.tm_vs : &p.tm_vw;
     if (lane == 0) mbar_expect_tx(full + s, (uint32_t)L.stage_bytes);
@@ -156,29 +144,21 @@ __device__ void il_chunk_mma(const DecodeParams& p, int b, int chunk, unsigned c
     for (int e = 0; e < 4; ++e) Oacc[i][e] = 0.f;
   }
 
-#ifdef FA_IL_TIMING
-  long long tick__ = clock64();
-#endif
   for (int t = 0; t < nt; ++t) {
     const int s = t % IL_STAGES;
     const int gt = t0 + t;
     const bool sink = gt < n_st;
     const int row0 = (sink ? gt : gt - n_st) * TR;
     const int valid = min(TR, (sink ? a.n_sink : a.n_win) - row0);
-    IL_TICK(0);
     mbar_wait(full + s, (uint32_t)(t / IL_STAGES) & 1u, dead, p.err);
-    IL_TICK(1);
     __syncthreads();   // everyone is done with tile t-1: its stage, the probabilities and alpha are free
-    IL_TICK(2);
     if (warp == IL_W - 1) issue(t + 2);
     const unsigned char* ks = ring + s * L.stage_bytes;
     const unsigned char* vs = ks + L.nbF * box_bytes;
     for (int g = warp; g < Hkv; g += IL_W)
       il_scores_softmax<T>(ks, qb, pm, pl, m_run, l_run, alpha, g, D, mtiles, valid, qpitch, ppitch, box_bytes, p.c2,
                            lane);
-    IL_TICK(3);
     __syncthreads();
-    IL_TICK(4);
     // ---- numerators: unit = (KV head, 16-dim tile) --------------------------------------------------
 #pragma unroll
     for (int i = 0; i < IL_U; ++i) {
@@ -201,7 +181,6 @@ __device__ void il_chunk_mma(const DecodeParams& p, int b, int chunk, unsigned c
         }
       }
     }
-    IL_TICK(5);
   }
   __syncthreads();
 

@@ -38,18 +38,6 @@ constexpr int WS_SREG = 56, WS_QREG = 200;   // registers per thread of the two 
 // score warps must not spill (with 222 KB of shared memory the L1 that would catch spills is tiny), the spectral
 // warps have time to spare
 
-#ifdef FA_PHASE_TIMING
-#define WS_TICK(i)                                                      \
-  do {                                                                  \
-    if (ticker__) {                                                     \
-      const long long now__ = clock64();                                \
-      atomicAdd(&g_phase_clk[i], (unsigned long long)(now__ - tick__)); \
-      tick__ = now__;                                                   \
-    }                                                                   \
-  } while (0)
-#else
-#define WS_TICK(i)
-#endif
 
 struct WsSmem {
   int ec, es, fnt, interp_hi, interp_lo, snode32, snode, pw, ptx, ptp, alpha, mx, lx, bars, slots, total;
@@ -202,14 +190,6 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
   if (wp < 8) {
     // =========================== spectral warps ================================================
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(WS_SREG));
-#ifdef FA_PHASE_TIMING
-#ifdef FA_TICK_S
-    const bool ticker__ = (tid == 0);
-#else
-    const bool ticker__ = false;
-#endif
-    long long tick__ = clock64();
-#endif
     const int nt1 = wp & 3, khalf = wp >> 2;
     // this chunk's verbatim-V partial starts from zero (the score warps add into it at the end)
     {
@@ -256,13 +236,11 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
       ph2[f] = phase_mod(centre2 % (uint64_t)T2, n, T2);
       d2[f] = phase_mod((uint64_t)(2 * J), n, T2);
     }
-    WS_TICK(10);
     for (int j = 0; j < nst; ++j) {
       const int buf = j & 1;
       __half* fh = fnt + (buf * 2 + 0) * FD * fpitch;
       __half* fl = fnt + (buf * 2 + 1) * FD * fpitch;
       if (j >= 2) mbar_wait(empty_sp + buf, ((j >> 1) - 1) & 1, dead, p.err);
-      WS_TICK(10);
       // ---- node basis: rotate the table to this super-tile's centre ------------------------------
       if (2 * np < N) {
         float rc[2], rs[2];
@@ -293,7 +271,6 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
         }
       }
       ws_group_sync(1);
-      WS_TICK(11);
       // ---- scores at the nodes: s_node[16 x HN] = Fn_t[16 x 2N] * w[2N x HN] -----------------------
       if (nt1 < NT) {
         // consecutive MMAs never share an accumulator: a dependent MMA would wait out the whole latency
@@ -325,7 +302,6 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
         }
       }
       ws_group_sync(1);
-      WS_TICK(12);
       {
         __half* sh_ = snode + (buf * 2 + 0) * 32 * 24;
         __half* sl_ = snode + (buf * 2 + 1) * 32 * 24;
@@ -339,7 +315,6 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(full_sp + buf);
-      WS_TICK(13);
     }
     __syncthreads();
     return;
@@ -347,14 +322,6 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
 
   // ============================= score warps ======================================================
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(WS_QREG));
-#ifdef FA_PHASE_TIMING
-#if defined(FA_IL_TIMING) || defined(FA_TICK_S)
-  const bool ticker__ = false;
-#else
-  const bool ticker__ = (tid == 256);
-#endif
-  long long tick__ = clock64();
-#endif
   const int qw = wp - 8, nt = qw & 3, half = qw >> 2;
   const bool act = nt < NT;
   const int sq = act ? nt / NTs : 0, ntl = nt - sq * NTs;   // sequence of this column tile, tile within the sequence
@@ -415,7 +382,6 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
   for (int i = 0; i < WS_MTV; ++i)
 #pragma unroll
     for (int e = 0; e < 4; ++e) Oacc[i][e] = 0.f;
-  WS_TICK(0);
 
   for (int st = 0; st < nst; ++st) {
     const int buf = st & 1;
@@ -434,7 +400,6 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
     if (act) {
       // ---- verbatim-dim scores from the K rows (needs only the K tile, so it comes first) -----------
       mbar_wait(full_slot + sK, parK, dead, p.err);
-      WS_TICK(2);
       const unsigned char* ks_ = slots + sK * L.slot_bytes;
 #pragma unroll
       for (int ks = 0; ks < WS_KS; ++ks) {
@@ -457,15 +422,11 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_slot + sK);
     }
-    WS_TICK(3);
     if (nt == 0) {   // refill the slot once every warp of this half has released it
       mbar_wait(empty_slot + sK, parK, dead, p.err);
-      WS_TICK(10);
       issue_tile(iK + 3);
-      WS_TICK(11);
     }
     mbar_wait(full_sp + buf, (st >> 1) & 1, dead, p.err);
-    WS_TICK(0);
     if (act) {
       // ---- add the node scores interpolated to this warp's 64 tokens ---------------------------------
       uint32_t bh[2], bl[2];
@@ -492,7 +453,6 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
         mma16816<__half>(sc[mt], ah, bh);
       }
     }
-    WS_TICK(1);
     // ---- softmax over the 128 tokens of the super-tile (both halves agree on the maximum) ----------
     float al0 = 1.f, al1 = 1.f;
     __half2 ph[4][2];   // probabilities rounded to fp16: (head 2tq, 2tq+1) of token rows gq and gq+8 per 16-token tile
@@ -541,7 +501,6 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
       lsum0 = lsum0 * al0 + s0;   // this thread's rows only; the lanes are added at the end
       lsum1 = lsum1 * al1 + s1;
       __syncwarp();
-      WS_TICK(4);
       // ---- project the probabilities onto the nodes: pt[16 x 8] = Interp^T[16 x 64] * P[64 x 8] ------
       uint32_t bp[4][2];
 #pragma unroll
@@ -569,7 +528,6 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
 #pragma unroll
         for (int e = 0; e < 4; ++e) pt_acc[e] = (pt_acc[e] + pt2[0][e]) + (pt2[1][e] + pt2[2][e]);
       }
-      WS_TICK(5);
       // ---- verbatim-V numerators -------------------------------------------------------------------
       uint32_t bp_lo[4][2];
       if constexpr (kBf16) {
@@ -603,7 +561,6 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
         for (int ks = 0; ks < 4; ++ks) ldsm_x2_t(bp_lo[ks], pwT + (16 * ks + (lane & 15)) * 8);
       }
       mbar_wait(full_slot + sV, parV, dead, p.err);
-      WS_TICK(6);
       const unsigned char* vs_ = slots + sV * L.slot_bytes;
 #pragma unroll
       for (int i = 0; i < WS_MTV; ++i) {
@@ -631,12 +588,9 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_slot + sV);
     }
-    WS_TICK(7);
     if (nt == v_issuer) {
       mbar_wait(empty_slot + sV, parV, dead, p.err);
-      WS_TICK(12);
       issue_tile(iV + 3);
-      WS_TICK(13);
     }
     // ---- hand the node-projected probabilities of the column tile to every score warp -------------
     if (act) {
@@ -664,7 +618,6 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
       }
     }
     ws_group_sync(7);
-    WS_TICK(8);
     // ---- g[2N x HN] += Fn_t^T[2N x 16] * pt[16 x HN]  (this warp's 16-row tiles) -------------------
     {
       uint32_t bf[4][2], bl[4][2];
@@ -710,7 +663,6 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty_sp + buf);
-    WS_TICK(9);
   }
 
   // ---- chunk partials ---------------------------------------------------------------------------
@@ -774,6 +726,3 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
   }
 }
 
-#ifdef FA_PHASE_TIMING
-#undef WS_TICK
-#endif

@@ -296,150 +296,153 @@ def decode_attn(q, k_sink, v_sink, k_win, v_win, k_mn, v_mn, k_coef, v_coef,
 
 
 class LayerCalls:
-    """The two per-step calls of one cached layer (fa_evict_step, fa_decode_attn) with everything that does
-    not change between decode steps bound once: base pointers, strides, tables, statistics and the argument
-    block.  A decode step then costs two ctypes calls and a handful of integer operations on the host instead
-    of a dozen tensor views and ~70 attribute writes."""
+    """The two per-step calls of one cached layer behind a library-side handle (``fa_layer_*``): buffers,
+    tables, statistics, planner switches and tensor maps are bound once when the layer is created, a decode
+    step passes the window offset, the span length and the new tensors only."""
 
     def __init__(self, kbuf, vbuf, k_unc, v_unc, k_coef, v_coef, stats32, tables, S, W, num_head_kv, T, mid_l0,
                  T_c, angle_mode, with_il=True):
         self.dev = kbuf.device
-        self.es = kbuf.element_size()
-        self.B, _, self.F = kbuf.shape
+        self.B, rows, self.F = kbuf.shape
         self.S, self.W, self.Hkv = int(S), int(W), int(num_head_kv)
         self.D = self.F // self.Hkv
-        self.dtype = _dt(kbuf)
         self.tables, self.stats32 = tables, stats32           # keep the tensors alive
         self.k_coef, self.v_coef = k_coef, v_coef
         self.kbuf, self.vbuf = kbuf, vbuf
-        self.kbuf_p, self.vbuf_p, self.buf_sb = kbuf.data_ptr(), vbuf.data_ptr(), kbuf.stride(0)
-        if vbuf.stride(0) != self.buf_sb or kbuf.stride(1) != self.F or kbuf.stride(2) != 1:
+        if vbuf.stride(0) != kbuf.stride(0) or kbuf.stride(1) != self.F or kbuf.stride(2) != 1 \
+                or vbuf.stride(1) != self.F or vbuf.stride(2) != 1:
             raise ValueError("K and V window buffers must be dense (B, rows, F) with equal strides")
-        self.T_c, self.angle_mode = int(T_c), int(angle_mode)
-        self.with_il = with_il
-        tb = tables
-        self.Mc_k, self.Mc_v = tb.kc_list.numel(), tb.vc_list.numel()
-        self.Mn_k, self.Mn_v = tb.kn_list.numel(), tb.vn_list.numel()
-        self.N = (k_coef if k_coef is not None else v_coef).shape[1] // 2 if (k_coef is not None or v_coef is not None) else 1
-        a = self.a = DecodeArgs()
-        a.B, a.Hkv, a.D = self.B, self.Hkv, self.D
-        a.n_sink = self.S if with_il else 0
-        a.n_win = self.W if with_il else 0
-        a.mid_l0, a.N, a.T = int(mid_l0), self.N, int(T)
-        a.Mc_k, a.Mc_v, a.Mn_k, a.Mn_v = self.Mc_k, self.Mc_v, self.Mn_k, self.Mn_v
-        a.dtype = self.dtype
-        if with_il:
-            a.k_sink, a.v_sink, a.sink_sb = self.kbuf_p, self.vbuf_p, self.buf_sb
-            a.win_sb = self.buf_sb
-        if k_coef is not None:
-            a.k_coef = k_coef.data_ptr()
-        if v_coef is not None:
-            a.v_coef = v_coef.data_ptr()
         for t in stats32:
             if t.dtype != torch.float32 or not t.is_contiguous():
                 raise ValueError("statistics must be contiguous float32")
-        (a.avg_k_u, a.avg_k_d, a.scale_k, a.avg_v_u, a.avg_v_d, a.scale_v) = [t.data_ptr() for t in stats32]
-        a.kc_list, a.kc_h, a.kn_list, a.kn_h = (tb.kc_list.data_ptr(), tb.kc_h.data_ptr(), tb.kn_list.data_ptr(),
+        self.with_il = with_il
+        tb = tables
+        d = self.desc = _lib.LayerDesc()
+        d.B, d.Hkv, d.D, d.S, d.W = self.B, self.Hkv, self.D, self.S, self.W
+        have = k_coef if k_coef is not None else v_coef
+        d.N = have.shape[1] // 2 if have is not None else 1
+        d.T, d.T_c, d.angle_mode, d.dtype, d.mid_l0 = int(T), int(T_c), int(angle_mode), _dt(kbuf), int(mid_l0)
+        d.Mc_k, d.Mc_v = tb.kc_list.numel(), tb.vc_list.numel()
+        d.Mn_k, d.Mn_v = tb.kn_list.numel(), tb.vn_list.numel()
+        d.with_il = 1 if with_il else 0
+        d.kbuf, d.vbuf, d.buf_sb, d.buf_rows = kbuf.data_ptr(), vbuf.data_ptr(), kbuf.stride(0), rows
+        d.k_coef = k_coef.data_ptr() if k_coef is not None else None
+        d.v_coef = v_coef.data_ptr() if v_coef is not None else None
+        (d.avg_k_u, d.avg_k_d, d.scale_k, d.avg_v_u, d.avg_v_d, d.scale_v) = [t.data_ptr() for t in stats32]
+        d.kc_list, d.kc_h, d.kn_list, d.kn_h = (tb.kc_list.data_ptr(), tb.kc_h.data_ptr(), tb.kn_list.data_ptr(),
                                                 tb.kn_h.data_ptr())
-        a.vc_list, a.vc_h, a.vn_list, a.vn_h = (tb.vc_list.data_ptr(), tb.vc_h.data_ptr(), tb.vn_list.data_ptr(),
+        d.vc_list, d.vc_h, d.vn_list, d.vn_h = (tb.vc_list.data_ptr(), tb.vc_h.data_ptr(), tb.vn_list.data_ptr(),
                                                 tb.vn_h.data_ptr())
-        a.kn_h_host = C.cast(tb.kn_h_host, C.c_void_p)
-        a.vn_h_host = C.cast(tb.vn_h_host, C.c_void_p)
-        self._aref = C.byref(a)
-        self._scratch_n_mid = -1      # n_mid the scratch size was last asked for
-        self.rebind(k_unc, v_unc)
+        d.kn_h_host = C.cast(tb.kn_h_host, C.c_void_p)
+        d.vn_h_host = C.cast(tb.vn_h_host, C.c_void_p)
+        self._set_stores(k_unc, v_unc)
+        h = C.c_void_p()
+        with torch.cuda.device(self.dev):
+            check(lib.fa_layer_create(C.byref(d), C.byref(h)), "fa_layer_create")
+        self._h = h
+        self._scratch_key = None
+        self._scratch_bytes = 0
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            lib.fa_layer_destroy(h)
+            self._h = None
+
+    def _set_stores(self, k_unc, v_unc):
+        self.k_unc, self.v_unc = k_unc, v_unc
+        d = self.desc
+        d.k_unc, d.v_unc = k_unc.data_ptr(), v_unc.data_ptr()
+        d.k_unc_sb, d.v_unc_sb = k_unc.stride(0), v_unc.stride(0)
+        d.k_unc_sk, d.v_unc_sk = max(k_unc.stride(1), d.Mn_k), max(v_unc.stride(1), d.Mn_v)
+        d.unc_rows = k_unc.shape[1]
+
+    def set_statistics(self, stats32):
+        """Replace the six float32 statistics tensors (avg_k_u, avg_k_d, scale_k, avg_v_u, avg_v_d, scale_v);
+        the handle is made anew around the same buffers."""
+        for t in stats32:
+            if t.dtype != torch.float32 or not t.is_contiguous():
+                raise ValueError("statistics must be contiguous float32")
+        self.stats32 = stats32
+        d = self.desc
+        (d.avg_k_u, d.avg_k_d, d.scale_k, d.avg_v_u, d.avg_v_d, d.scale_v) = [t.data_ptr() for t in stats32]
+        lib.fa_layer_destroy(self._h)
+        h = C.c_void_p()
+        with torch.cuda.device(self.dev):
+            check(lib.fa_layer_create(C.byref(d), C.byref(h)), "fa_layer_create")
+        self._h = h
+        self._scratch_key = None
 
     def rebind(self, k_unc, v_unc):
         """(Re)attach the verbatim stores (they are reallocated when they grow)."""
-        self.k_unc, self.v_unc = k_unc, v_unc
-        self.k_unc_p, self.v_unc_p = k_unc.data_ptr(), v_unc.data_ptr()
-        a = self.a
-        a.k_mn, a.k_mn_sb, a.k_mn_sk = self.k_unc_p, k_unc.stride(0), max(k_unc.stride(1), self.Mn_k)
-        a.v_mn, a.v_mn_sb, a.v_mn_sk = self.v_unc_p, v_unc.stride(0), max(v_unc.stride(1), self.Mn_v)
-        self.k_unc_sk, self.v_unc_sk = k_unc.stride(1), v_unc.stride(1)
+        self._set_stores(k_unc, v_unc)
+        d = self.desc
+        check(lib.fa_layer_rebind_stores(self._h, d.k_unc, d.v_unc, d.k_unc_sb, d.v_unc_sb, d.k_unc_sk, d.v_unc_sk,
+                                         d.unc_rows), "fa_layer_rebind_stores")
+        self._scratch_key = None
 
     def step(self, off, n_mid, phase, k_new, v_new, appends=True):
-        """fa_evict_step for the window row at offset ``off``: its compressed dims go into the coefficients
-        at ``phase``, its verbatim dims to row ``n_mid`` of the stores, the new token behind the window."""
+        """One steady-state cache step: the window row at offset ``off`` is evicted (its compressed dims go into
+        the coefficients at ``phase``, its verbatim dims to row ``n_mid`` of the stores) and the new token is
+        written behind the window."""
         if k_new.dim() == 4:
             k_new, v_new = k_new[:, :, 0], v_new[:, :, 0]
         if k_new.stride(2) != 1 or v_new.stride() != k_new.stride():
-            raise ValueError("fa_evict_step: K and V must share strides and have a contiguous last dimension")
-        es, F = self.es, self.F
-        row_b = (self.S + off) * F * es
-        dst_b = row_b + self.W * F * es
-        k_ev, v_ev = self.kbuf_p + row_b, self.vbuf_p + row_b
-        tb = self.tables
-        mn_k, mn_v = (self.Mn_k, self.Mn_v) if appends else (0, 0)
-        rc = lib.fa_evict_step(self.a.k_coef if self.Mc_k else None, k_ev, self.buf_sb, tb.kc_list.data_ptr(), self.Mc_k,
-                               self.a.v_coef if self.Mc_v else None, v_ev, self.buf_sb, tb.vc_list.data_ptr(), self.Mc_v,
-                               self.N, int(phase), self.T_c, self.angle_mode,
-                               k_ev, v_ev, self.buf_sb, tb.kn_list.data_ptr(), mn_k, tb.vn_list.data_ptr(), mn_v,
-                               self.k_unc_p + n_mid * self.k_unc_sk * es, self.a.k_mn_sb,
-                               self.v_unc_p + n_mid * self.v_unc_sk * es, self.a.v_mn_sb,
-                               k_new.data_ptr(), v_new.data_ptr(), k_new.stride(0), k_new.stride(1),
-                               self.kbuf_p + dst_b, self.vbuf_p + dst_b, self.buf_sb,
-                               self.dtype, self.B, self.Hkv, self.D, torch.cuda.current_stream(self.dev).cuda_stream)
+            raise ValueError("fa_layer_update: K and V must share strides and have a contiguous last dimension")
+        if torch.cuda.current_device() != self.dev.index:
+            torch.cuda.set_device(self.dev)
+        rc = lib.fa_layer_update(self._h, off, n_mid, int(phase), 1 if appends else 0, k_new.data_ptr(),
+                                 v_new.data_ptr(), k_new.stride(0), k_new.stride(1),
+                                 torch.cuda.current_stream(self.dev).cuda_stream)
         if rc:
-            check(rc, "fa_evict_step")
+            check(rc, "fa_layer_update")
         _count(1)
 
     def attend(self, q, off, n_mid, num_head_q, sm_scale=-1.0, phase_events=None, return_lse=False):
-        """fa_decode_attn of one query token per sequence; ``q``: (B, Hq*D).  Returns (B, Hq, D) float32."""
+        """Decode attention of one query token per sequence; ``q``: (B, Hq*D).  Returns (B, Hq, D) float32
+        (plus the softmax statistics (m, l) with ``return_lse``)."""
         global last_decode_path
-        a = self.a
         if q.stride(1) != 1 or q.dtype != self.kbuf.dtype:
             raise ValueError("q must have the cache dtype and a contiguous last dimension")
-        a.Hq = num_head_q
-        a.sm_scale = float(sm_scale) if sm_scale is not None else -1.0
-        a.q, a.q_sb = q.data_ptr(), q.stride(0)
-        a.n_mid = n_mid
-        if self.with_il:
-            win_b = (self.S + off) * self.F * self.es
-            a.k_win, a.v_win = self.kbuf_p + win_b, self.vbuf_p + win_b
         out = torch.empty((self.B, num_head_q, self.D), dtype=torch.float32, device=self.dev)
-        a.out = out.data_ptr()
         m = l = None
         if return_lse:
             m = torch.empty((self.B, num_head_q), dtype=torch.float32, device=self.dev)
             l = torch.empty_like(m)
-            a.m_out, a.l_out = m.data_ptr(), l.data_ptr()
-        else:
-            a.m_out = a.l_out = None
-        if phase_events is not None:
-            ev = (C.c_void_p * 5)(*[(e.cuda_event if e is not None else None) for e in phase_events])
-            a.phase_events_host = C.cast(ev, C.c_void_p)
-        else:
-            a.phase_events_host = None
-        stream = torch.cuda.current_stream(self.dev).cuda_stream
+        if n_mid == 0 and not self.with_il:
+            # this rank holds no key at all (a span slice with no rows): an empty partial result that the
+            # log-sum-exp merge ignores (l = 0), so that the rank still takes part in the exchange
+            out.zero_()
+            if return_lse:
+                m.fill_(-1.0e30)
+                l.zero_()
+            return (out, m, l) if return_lse else out
         if torch.cuda.current_device() != self.dev.index:
             torch.cuda.set_device(self.dev)
-        # the plan (and with it the scratch need) moves only when n_mid crosses a tile boundary: ask again every
-        # 32 steps, keep twice what was asked, and ask at once if the library says the buffer is too small
-        if self._scratch_n_mid < 0 or n_mid - self._scratch_n_mid >= 32 or n_mid < self._scratch_n_mid:
-            self._query_scratch()
+        stream = torch.cuda.current_stream(self.dev).cuda_stream
+        # the plan (and with it the scratch need) is constant while n_mid stays inside one 128-token super-tile
+        key = (num_head_q, (n_mid + 127) >> 7)
+        if key != self._scratch_key:
+            nbytes = lib.fa_layer_scratch_bytes(self._h, num_head_q, n_mid)
+            if nbytes == 0:
+                check(lib.fa_layer_attend(self._h, off, n_mid, num_head_q, q.data_ptr(), q.stride(0), -1.0,
+                                          out.data_ptr(), None, None, None, 0, None, stream), "fa_layer_attend")
+                raise RuntimeError("fa_layer_attend: empty scratch plan")
+            self._scratch_bytes = 2 * int(nbytes)
+            self._scratch_key = key
+            last_decode_path = lib.fa_layer_decode_path(self._h)
         sc = scratch(self.dev, self._scratch_bytes)
-        a.scratch, a.scratch_bytes = sc.data_ptr(), sc.numel()
-        rc = lib.fa_decode_attn(self._aref, stream)
-        if rc == -5:      # FA_ERR_CAPACITY: the plan changed under a stale scratch size
-            self._query_scratch()
-            sc = scratch(self.dev, self._scratch_bytes)
-            a.scratch, a.scratch_bytes = sc.data_ptr(), sc.numel()
-            rc = lib.fa_decode_attn(self._aref, stream)
+        ev = None
+        if phase_events is not None:
+            ev = (C.c_void_p * 5)(*[(e.cuda_event if e is not None else None) for e in phase_events])
+        rc = lib.fa_layer_attend(self._h, off, n_mid, num_head_q, q.data_ptr(), q.stride(0),
+                                 float(sm_scale) if sm_scale is not None else -1.0, out.data_ptr(),
+                                 m.data_ptr() if m is not None else None, l.data_ptr() if l is not None else None,
+                                 sc.data_ptr(), sc.numel(), ev, stream)
         if rc:
-            check(rc, "fa_decode_attn")
+            check(rc, "fa_layer_attend")
         _count(3 if n_mid > 0 else 2)
         return (out, m, l) if return_lse else out
-
-    def _query_scratch(self):
-        global last_decode_path
-        nbytes = lib.fa_decode_scratch_bytes(self._aref)
-        if nbytes == 0:
-            check(lib.fa_decode_attn(self._aref, None), "fa_decode_attn")   # reports the plan error
-            raise RuntimeError("fa_decode_attn: empty scratch plan")
-        self._scratch_bytes = 2 * int(nbytes)
-        self._scratch_n_mid = self.a.n_mid
-        last_decode_path = lib.fa_decode_path(self._aref)
 
 
 def merge(o, m, l):

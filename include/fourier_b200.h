@@ -216,6 +216,61 @@ int fa_decode_attn(const fa_decode_args_t* args_host, fa_stream_t stream);
 #define FA_DECODE_STATIC_SCRATCH_BYTES (24u << 20)
 int fa_decode_attn_static(const fa_decode_args_t* args_host, fa_stream_t stream);
 
+/* ---- layer handle: the per-step calls of one cached layer with everything static bound once --------
+ * Replaces, per decode step and layer, the steady-state branch of DynamicCache.update (CU:731-748) and the
+ * Fourier branch of LlamaSdpaAttention.forward (ML:641-660: the two torch.cat of sinks and window and the
+ * call of triton_fourier_attn, KM:684-779).  The reference rebuilds every view and re-reads every attribute
+ * on each step in Python; here the buffers, tables, statistics and tensor maps of a layer are bound when the
+ * handle is made and a step passes integers only.
+ *
+ *   kbuf / vbuf : (B, buf_rows, Hkv*D) dense rows, batch stride buf_sb; rows [0, S) are the sinks, the
+ *                 window is the W rows starting at row S + win_off (0 <= win_off <= W), a new token is
+ *                 written at row S + win_off + W; buf_rows >= S + 2W.  Rows the window has not reached yet
+ *                 must hold finite values (zeros).
+ *   k_unc/v_unc : (B, unc_rows, Mn_*) verbatim stores over their whole capacity, row strides *_unc_sk, batch
+ *                 strides *_unc_sb; rows [0, n_mid) are live, the rest must hold finite values (zeros).
+ *   statistics, tables: as in fa_decode_args_t.  with_il = 0 leaves sinks and window to another rank
+ *                 (sequence split).  mid_l0: span position of row 0 of the stores.
+ * The planner switches FA_DECODE_EXACT / FA_DECODE_NO_WS are read when the handle is created. */
+typedef struct fa_layer fa_layer_t;
+typedef struct {
+  int32_t B, Hkv, D, S, W, N, T, T_c, angle_mode, dtype, mid_l0;
+  int32_t Mc_k, Mn_k, Mc_v, Mn_v;
+  int32_t with_il;
+  void *kbuf, *vbuf;
+  int64_t buf_sb;
+  int32_t buf_rows;
+  void *k_unc, *v_unc;
+  int64_t k_unc_sb, v_unc_sb, k_unc_sk, v_unc_sk;
+  int32_t unc_rows;
+  float *k_coef, *v_coef;
+  const float *avg_k_u, *avg_k_d, *scale_k, *avg_v_u, *avg_v_d, *scale_v;
+  const int32_t *kc_list, *kc_h, *kn_list, *kn_h, *vc_list, *vc_h, *vn_list, *vn_h;
+  const int32_t *kn_h_host, *vn_h_host; /* HOST copies of kn_h / vn_h (Hkv + 1 entries), kept by the caller */
+} fa_layer_desc_t;
+
+int fa_layer_create(const fa_layer_desc_t* desc_host, fa_layer_t** out);
+void fa_layer_destroy(fa_layer_t* layer);
+/* the verbatim stores were reallocated (they grew) */
+int fa_layer_rebind_stores(fa_layer_t* layer, void* k_unc, void* v_unc, int64_t k_unc_sb, int64_t v_unc_sb,
+                           int64_t k_unc_sk, int64_t v_unc_sk, int32_t unc_rows);
+/* One steady-state cache step (= fa_evict_step on the layer's buffers): the window row at offset win_off is
+ * evicted -- its compressed dims go into the coefficients at `phase`, its verbatim dims to row n_mid of the
+ * stores (appends != 0) -- and the new token (element (b, h, d) at b*new_sb + h*new_sh + d) is written
+ * behind the window.  Afterwards the window starts at win_off + 1 and the span holds n_mid + 1 rows. */
+int fa_layer_update(fa_layer_t* layer, int32_t win_off, int32_t n_mid, int64_t phase, int32_t appends,
+                    const void* k_new, const void* v_new, int64_t new_sb, int64_t new_sh, fa_stream_t stream);
+/* Scratch fa_layer_attend needs for Hq query heads at span length n_mid (constant while n_mid stays inside
+ * one 128-token super-tile). */
+size_t fa_layer_scratch_bytes(fa_layer_t* layer, int32_t Hq, int32_t n_mid);
+/* Decode attention of one query token per sequence (= fa_decode_attn on the layer's state): q (B, Hq*D) with
+ * batch stride q_sb, out (B, Hq, D) fp32, m_out / l_out (B, Hq) or null. */
+int fa_layer_attend(fa_layer_t* layer, int32_t win_off, int32_t n_mid, int32_t Hq, const void* q, int64_t q_sb,
+                    float sm_scale, float* out, float* m_out, float* l_out, void* scratch, size_t scratch_bytes,
+                    void* const* phase_events_host, fa_stream_t stream);
+/* middle-span pass the last plan of this layer chose (see fa_decode_path) */
+int fa_layer_decode_path(fa_layer_t* layer);
+
 /* Log-sum-exp merge of n_parts partial results (KM:756-776), e.g. one per device of a
  * sequence split:  out = sum_i o_i l_i 2^(m_i - m*) / sum_i l_i 2^(m_i - m*),
  * with o_i the NORMALISED partial outputs (rows, D), m_i/l_i (rows).  parts are stacked:

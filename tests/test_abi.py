@@ -32,20 +32,22 @@ def test_every_declared_symbol_is_exported(L):
     assert L.lib.fa_version() >= 100
 
 
-def test_argument_block_layout_matches_c(L):
-    fields = [f[0] for f in L.DecodeArgs._fields_]
-    prog = '#include <stdio.h>\n#include <stddef.h>\n#include "fourier_b200.h"\nint main(){printf("%zu\\n", sizeof(fa_decode_args_t));\n'
+@pytest.mark.parametrize("ctype,pytype", [("fa_decode_args_t", "DecodeArgs"), ("fa_layer_desc_t", "LayerDesc")])
+def test_argument_block_layout_matches_c(L, ctype, pytype):
+    mirror = getattr(L, pytype)
+    fields = [f[0] for f in mirror._fields_]
+    prog = '#include <stdio.h>\n#include <stddef.h>\n#include "fourier_b200.h"\nint main(){printf("%zu\\n", sizeof(' + ctype + '));\n'
     for f in fields:
-        prog += f'printf("%zu\\n", offsetof(fa_decode_args_t, {f}));\n'
+        prog += f'printf("%zu\\n", offsetof({ctype}, {f}));\n'
     prog += "return 0;}\n"
     with tempfile.TemporaryDirectory() as d:
         src, exe = os.path.join(d, "t.c"), os.path.join(d, "t")
         open(src, "w").write(prog)
         subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), src, "-o", exe])
         vals = [int(x) for x in subprocess.check_output([exe]).split()]
-    assert vals[0] == C.sizeof(L.DecodeArgs)
+    assert vals[0] == C.sizeof(mirror)
     for f, off in zip(fields, vals[1:]):
-        assert getattr(L.DecodeArgs, f).offset == off, f
+        assert getattr(mirror, f).offset == off, f
 
 
 def _args(L, **kw):
@@ -96,3 +98,24 @@ def test_scratch_size_queries(L):
     assert L.lib.fa_compress_scratch_bytes(1, 1, 128, 768, 1024) == 0
     assert L.lib.fa_compress_scratch_bytes(1, 31740, 256, 768, 1024) > 0
     assert L.lib.fa_recon_stats_scratch_bytes(8, 31740, 768) > 0
+
+
+def test_layer_handle_validation_without_a_gpu(L):
+    """fa_layer_create checks sizes and pointers on the host; the handle plans without touching a device."""
+    h = C.c_void_p()
+    d = L.LayerDesc()
+    assert L.lib.fa_layer_create(C.byref(d), C.byref(h)) == -2
+    assert L.lib.fa_layer_create(None, C.byref(h)) == -1
+    for k, v in dict(B=8, Hkv=8, D=128, S=4, W=1024, N=256, T=31996, T_c=31995, angle_mode=1, dtype=1, Mc_k=768,
+                     Mn_k=256, Mc_v=768, Mn_v=256, with_il=1, kbuf=4096, vbuf=8192, buf_sb=2052 * 1024, buf_rows=2052,
+                     k_unc=4096, v_unc=4096, k_unc_sb=32004 * 256, v_unc_sb=32004 * 256, k_unc_sk=256, v_unc_sk=256,
+                     unc_rows=32004).items():
+        setattr(d, k, v)
+    assert L.lib.fa_layer_create(C.byref(d), C.byref(h)) == 0 and h.value
+    n0 = L.lib.fa_layer_scratch_bytes(h, 32, 31740)
+    assert n0 > 0
+    # the plan, and with it the scratch need, stays put while n_mid grows inside one 128-token super-tile
+    assert all(L.lib.fa_layer_scratch_bytes(h, 32, n) == n0 for n in range(31617, 31745))
+    assert L.lib.fa_layer_update(h, 1024, 31740, 31741, 1, None, None, 0, 0, None) == -2      # window offset out of range
+    assert L.lib.fa_layer_update(h, 0, 32004, 31741, 1, None, None, 0, 0, None) == -5         # stores are full
+    L.lib.fa_layer_destroy(h)

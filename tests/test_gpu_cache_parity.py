@@ -49,9 +49,8 @@ def test_golden_case(name):
         assert _ulp_close(host(t), z[nm], rel), nm
     # decode with the reference's statistics so that a one-ulp flip there cannot mask (or fake) an
     # error of the attention kernel; the statistics themselves were compared just above
-    st = cache._state[0]
-    st.stats32 = tuple(dev(np.asarray(z[nm], np.float32)) for nm in
-                       ("k_layer_average", "kd_layer_average", "k_scale", "v_layer_average", "vd_layer_average", "v_scale"))
+    cache.set_layer_statistics(0, tuple(dev(np.asarray(z[nm], np.float32)) for nm in (
+        "k_layer_average", "kd_layer_average", "k_scale", "v_layer_average", "vd_layer_average", "v_scale")))
     for s in range(g["steps"]):
         kd, vd = cache.update(update_arg(k[:, :, P + s:P + s + 1], dt), update_arg(v[:, :, P + s:P + s + 1], dt), 0)
         assert kd["k_init"] is not None

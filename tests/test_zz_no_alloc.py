@@ -14,28 +14,51 @@ import pytest
 import torch
 
 from tests.gpu_util import decode_inputs_from_oracle, dev, host
-from tests.test_gpu_kernels import DECODE_CASES, _state
+from tests.test_gpu_kernels import DECODE_CASES, FAST_CASES, _state
 
 pytestmark = pytest.mark.gpu
 
 
 def _both(name):
     import fourierattention_b200.ops as ops
-    g = DECODE_CASES[name]
+    g = DECODE_CASES[name] if name in DECODE_CASES else FAST_CASES[name]
     oc, q = _state(g)
     inp = decode_inputs_from_oracle(oc, g["dtype"])
     kw = dict(num_head_q=g["Hq"], num_head_kv=g["Hkv"], T=oc.T, return_lse=True, **inp)
     want = ops.decode_attn(dev(q, g["dtype"]), **kw)
     got = ops.decode_attn(dev(q, g["dtype"]), static_scratch=True, **kw)
+    path = ops.last_decode_path
     torch.cuda.synchronize()
-    return want, got
+    ideal = oc.attend(q, 0, g["Hq"], g["Hkv"], faithful=False)[:, :, 0]
+    return want, got, path, ideal
 
 
 def test_static_scratch_matches_on_two_calls_in_a_row():
+    """The comparison is with the ordinary entry point, which the other test files hold to the oracle on
+    these same cases; the float64 oracle result is checked here as well, loosely, so that this file also
+    stands on its own."""
     for name in ("wide", "gqa3_bf16", "wide"):
-        want, got = _both(name)
+        want, got, path, ideal = _both(name)
+        assert path == 0
         for w, g_ in zip(want, got):
             assert np.abs(host(w) - host(g_)).max() <= 2e-6, name
+        assert np.abs(host(got[0]) - ideal).max() <= 3e-5 * max(1.0, np.abs(ideal).max())
+
+
+def test_static_scratch_on_the_tensor_core_passes_with_changing_plans():
+    """The shared buffer keeps whatever the previous call left in it, and consecutive calls here have
+    different chunk counts, batch sizes and sequences per CTA (a warp-specialised plan, an exact-kernel
+    plan, a warp-specialised plan that packs four sequences per CTA with a batch of five, a 64-token
+    super-tile plan): every word a call reads must have been written by that same call."""
+    seen = set()
+    for name in ("fast_32heads_fp16", "wide", "fast_packed_4seq", "fast_gqa3_half_tiles", "fast_packed_2seq",
+                 "gqa3_bf16", "fast_llama8b_layer", "fast_packed_4seq"):
+        want, got, path, ideal = _both(name)
+        seen.add(path)
+        for w, g_ in zip(want, got):
+            assert np.abs(host(w) - host(g_)).max() <= 2e-6, name
+        assert np.abs(host(got[0]) - ideal).max() <= 1.5e-4 * max(1.0, np.abs(ideal).max()), name
+    assert seen == {0, 1, 2}, seen
 
 
 def test_static_scratch_allocates_nothing_and_rejects_oversize():
