@@ -31,15 +31,23 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # BASELINE config 2: the configuration the headline metric is quoted on
+    # the headline workload: full Llama-3.1-8B attention geometry, batch 8, 32k-token prompts, 256 decode steps
     "llama31_8b_32k": dict(layers=32, B=8, Hq=32, Hkv=8, D=128, ctx=32768, S=4, W=1024, M=512, ncomp=96,
                            dtype="bf16", new_tokens=256),
-    # BASELINE config 3
+    # Llama-3.2-3B attention geometry, batch 32, 16k-token prompts
     "llama32_3b_16k": dict(layers=28, B=32, Hq=24, Hkv=8, D=128, ctx=16384, S=4, W=512, M=256, ncomp=80,
                            dtype="bf16", new_tokens=256),
-    # BASELINE config 1 (single layer, fp16)
+    # one layer, one sequence, fp16, 8k context, 64 decode steps
     "single_layer_8k": dict(layers=1, B=1, Hq=32, Hkv=8, D=128, ctx=8192, S=4, W=1024, M=256, ncomp=96,
                             dtype="fp16", new_tokens=64),
+    # one long sequence, one layer, 2048-token window, M = 1024; with --gpus N the middle span is split by
+    # sequence over the N ranks and the partial results are merged by log-sum-exp over NCCL
+    "long_131k": dict(layers=1, B=1, Hq=32, Hkv=8, D=128, ctx=131072, S=4, W=2048, M=1024, ncomp=96,
+                      dtype="bf16", new_tokens=256, seq_split=True),
+    "long_262k": dict(layers=1, B=1, Hq=32, Hkv=8, D=128, ctx=262144, S=4, W=2048, M=1024, ncomp=96,
+                      dtype="bf16", new_tokens=256, seq_split=True),
+    "long_524k": dict(layers=1, B=1, Hq=32, Hkv=8, D=128, ctx=524288, S=4, W=2048, M=1024, ncomp=96,
+                      dtype="bf16", new_tokens=256, seq_split=True),
     # a small case for profiler captures (a few hundred MB on the device, still larger than L2)
     "profile_small": dict(layers=2, B=8, Hq=32, Hkv=8, D=128, ctx=32768, S=4, W=1024, M=512, ncomp=96,
                           dtype="bf16", new_tokens=256),
@@ -82,7 +90,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                          "-lms", "20", "-i", str(self.gpu)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -162,16 +170,100 @@ def reference_arm(args, w):
     if rank != 0:
         return
     cores = os.cpu_count() or 1
-    t, sample = run_cpu_oracle(w, max(1, args.steps), max(0, args.warmup))
-    step_s = t * w["layers"] * w["B"]           # one full step = every layer and sequence
+    steps = max(1, args.steps)
+    t, sample = run_cpu_oracle(w, steps, max(0, args.warmup))
+    scale = w["layers"] * w["B"]                # one full step = every layer and sequence
+    step_s = t * scale
     val = w["B"] / step_s
     line = {"impl": "reference", "metric": "decode-attn tokens/s", "value": val, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": w["dtype"],
             "data": "synthetic", "config": workload_config(args, w),
-            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+            # what was timed is one layer x one sequence; the full step is that time x layers x batch
+            "extrapolated": True, "sampled_s": t * steps, "sampled_ms_per_sample_step": t * 1e3, "scale": scale,
+            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample,
+                             "extrapolated": True, "sampled_s": t * steps, "scale": scale},
             "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+def triton_arm(args, w):
+    """Context number, not a target: the reference's own GPU path -- its unmodified ``DynamicCache.update`` and
+    ``triton_fourier_attn`` (fourier_triton_valid4_v2.py:684-779), JIT-compiled by the installed Triton -- timed
+    on ONE layer of the workload after warm-up; the full step is that time x layers.  It needs a checkout of the
+    reference (``--reference-dir`` or FA_REFERENCE_DIR, the directory that holds ``fourier_attn_triton/``);
+    without one, or if its modules do not import or run on this box, the line says ``unavailable`` and why."""
+    ref = args.reference_dir or os.environ.get("FA_REFERENCE_DIR") or ""
+    base = {"impl": "triton", "metric": "decode-attn tokens/s", "unit": "tokens/s", "n_gpus": 1,
+            "config": workload_config(args, w)}
+    src = os.path.join(ref, "fourier_attn_triton")
+    if not ref or not os.path.isdir(src):
+        print(json.dumps(dict(base, unavailable=f"no reference checkout at {src!r}")), flush=True)
+        return
+    try:
+        import torch
+        for name in ("matplotlib", "matplotlib.pyplot"):          # imported at the top of the kernel module, unused
+            sys.modules.setdefault(name, types.ModuleType(name))
+        sys.path.insert(0, src)
+        import fourier_triton_valid4_v2 as km
+        sys.modules["lxr_fourier_triton_valid4_v2"] = km
+        import cache_utils_fourier as cu
+        from fourierattention_b200 import synth                      # seeded inputs only; none of its kernels run here
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        tdt = torch.bfloat16 if w["dtype"] == "bf16" else torch.float16
+        W_, K_ = max(2, args.warmup), args.steps
+        tables = synth.make_splithead_tables(1, w["Hkv"], w["D"], w["ncomp"], seed=2024)
+        tf = tempfile.NamedTemporaryFile("w", suffix=".json", delete=False)
+        json.dump(tables, tf); tf.close()
+        cfg = types.SimpleNamespace(numinittokens=w["S"], maxlocallen=w["W"], maxmidstates=w["M"],
+                                    non_critical_dims_path=tf.name, max_position_embeddings=1 << 30,
+                                    num_key_value_heads=w["Hkv"], max_new_tokens=max(w["new_tokens"], W_ + K_ + 1),
+                                    model_type="llama")
+        cache = cu.DynamicCache(cfg)
+        os.unlink(tf.name)
+        B, D, Hq, Hkv = w["B"], w["D"], w["Hq"], w["Hkv"]
+        gen = torch.Generator(device=dev); gen.manual_seed(99)
+        k, v = synth.rope_kv(B, Hkv, w["ctx"], D, tdt, dev, gen)
+        cache.update(k.contiguous().transpose(1, 2).contiguous().transpose(1, 2), v.contiguous().transpose(1, 2).contiguous().transpose(1, 2), 0)
+        del k, v
+        mk = lambda s_: torch.randn(s_, device=dev, dtype=torch.float32, generator=gen).to(tdt)
+        n = W_ + K_
+        q, kn, vn = mk((n, B, 1, Hq * D)), mk((n, B, 1, Hkv, D)), mk((n, B, 1, Hkv, D))
+
+        def step(s_):
+            ks, vs = cache.update(kn[s_].transpose(1, 2), vn[s_].transpose(1, 2), 0)
+            return km.triton_fourier_attn(
+                q=q[s_].contiguous(), k_il=torch.cat([ks["k_init"], ks["k_local"]], dim=1).contiguous(),
+                v_il=torch.cat([vs["v_init"], vs["v_local"]], dim=1).contiguous(),
+                k_mc=ks["k_compressed"], v_mc=vs["v_compressed"], k_mn=ks["k_uncompressed"], v_mn=vs["v_uncompressed"],
+                avg_k_u=cache.k_layer_average[0], avg_k_d=cache.kd_layer_average[0], scale_k=cache.k_scale[0],
+                avg_v_u=cache.v_layer_average[0], avg_v_d=cache.vd_layer_average[0], scale_v=cache.v_scale[0],
+                kc_list=cache.k_non_critical_dims[0], kc_h_list=cache.k_non_critical_head_dims[0],
+                kn_list=cache.k_critical_dims[0], kn_h_list=cache.k_critical_head_dims[0],
+                vc_list=cache.v_non_critical_dims[0], vc_h_list=cache.v_non_critical_head_dims[0],
+                vn_list=cache.v_critical_dims[0], vn_h_list=cache.v_critical_head_dims[0],
+                num_head_q=Hq, num_head_kv=Hkv, seq_len_m=ks["k_uncompressed"].size(1),
+                T=cache.maxtokens - cache.numinittokens - cache.maxlocallen)
+        for s_ in range(W_):
+            out = step(s_)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s_ in range(W_, W_ + K_):
+            out = step(s_)
+        e1.record()
+        torch.cuda.synchronize()
+        layer_ms = e0.elapsed_time(e1) / K_
+        step_ms = layer_ms * w["layers"]
+        print(json.dumps(dict(base, value=B / (step_ms * 1e-3), ms_per_step=step_ms, steps=K_, warmup=W_,
+                              higher_is_better=True, dtype=w["dtype"], data="synthetic", extrapolated=w["layers"] > 1,
+                              sampled_ms_per_layer=layer_ms, scale=w["layers"],
+                              finite=bool(torch.isfinite(out.float()).all()),
+                              note="the reference's Triton path on this GPU, one layer timed, for context only")),
+              flush=True)
+    except Exception as ex:      # the context arm must never take the benchmark down
+        print(json.dumps(dict(base, unavailable=f"{type(ex).__name__}: {ex}"[:400])), flush=True)
 
 
 def workload_config(args, w):
@@ -202,6 +294,8 @@ def ours_arm(args, w):
     import fourierattention_b200 as pkg
     from fourierattention_b200 import ops, synth
 
+    if w.get("seq_split"):
+        return seq_split_arm(args, w, world, rank, dev)
     assert w["Hkv"] % world == 0, "KV heads must divide across ranks"
     hk = w["Hkv"] // world
     h0, h1 = rank * hk, (rank + 1) * hk
@@ -373,10 +467,112 @@ def ours_arm(args, w):
                 t, sample = run_cpu_oracle(w, 4, 1)
                 cpu_step = t * L * B
                 line["cpu_baseline"] = {"value": B / cpu_step, "unit": "tokens/s", "cores": os.cpu_count() or 1,
-                                        "kind": "port", "sample": sample}
+                                        "kind": "port", "sample": sample, "extrapolated": True,
+                                        "sampled_s": t * 4, "scale": L * B}
             except Exception as ex:  # the GPU result stands even if the host baseline cannot run
                 line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": os.cpu_count() or 1,
                                         "kind": "port", "sample": f"failed: {ex}"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def seq_split_arm(args, w, world, rank, dev):
+    """One long sequence, one layer: the middle span is split by sequence over the ranks (every rank keeps an
+    equal slice of the verbatim rows, the coefficients are replicated, rank 0 also attends sinks + window); a
+    step is ``update`` + attention, whose partial results travel in one all_gather of Hq*(D+2) floats per
+    rank and are merged by log-sum-exp on every rank.  Reports tokens/s, the bytes each GPU streams per step
+    as GB/s, and the share of a step that the exchange (all_gather + merge) takes, measured as the difference
+    to the same steps without it."""
+    import torch
+    import torch.distributed as dist
+    import fourierattention_b200 as pkg
+    from fourierattention_b200 import ops, synth
+    tdt = torch.bfloat16 if w["dtype"] == "bf16" else torch.float16
+    W_, K_ = args.warmup, args.steps
+    total_new = 2 * (W_ + K_) + 1
+    new_tokens = max(w["new_tokens"], total_new)
+    tables = synth.make_splithead_tables(1, w["Hkv"], w["D"], w["ncomp"], seed=2024)
+    tf = tempfile.NamedTemporaryFile("w", suffix=".json", delete=False)
+    json.dump(tables, tf); tf.close()
+    cfg = types.SimpleNamespace(numinittokens=w["S"], maxlocallen=w["W"], maxmidstates=w["M"],
+                                non_critical_dims_path=tf.name, max_position_embeddings=1 << 30,
+                                num_key_value_heads=w["Hkv"], max_new_tokens=new_tokens, model_type="llama")
+    cache = pkg.DynamicCache(cfg, device=dev, seq_shard=(rank, world) if world > 1 else None)
+    os.unlink(tf.name)
+    B, D, Hq, Hkv = w["B"], w["D"], w["Hq"], w["Hkv"]
+    gen = torch.Generator(device=dev); gen.manual_seed(99)          # every rank sees the same sequence
+    k, v = synth.rope_kv(B, Hkv, w["ctx"], D, tdt, dev, gen)
+    cache.update(k, v, 0)
+    del k, v
+    torch.cuda.synchronize()
+    n = 2 * (W_ + K_)
+    mk = lambda s_: torch.randn(s_, device=dev, dtype=torch.float32, generator=gen).to(tdt)
+    q, kn, vn = mk((n, B, Hq * D)), mk((n, B, Hkv, 1, D)), mk((n, B, Hkv, 1, D))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run(s0, count, merged):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for s_ in range(s0, s0 + count):
+            cache.update(kn[s_], vn[s_], 0)
+            if merged or world == 1:
+                cache.fourier_attention(q[s_], 0, Hq)
+            else:
+                cache.partial_attention(q[s_], 0, Hq)
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1)
+
+    run(0, W_, True)
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    time.sleep(0.2)
+    launches0 = ops.launch_count
+    wall0 = time.time()
+    ms = run(W_, K_, True)
+    wall1 = time.time()
+    launches = ops.launch_count - launches0
+    clocks = sampler.stop(wall0, wall1)
+    run(W_ + K_, W_, False)
+    ms_nox = run(2 * W_ + K_, K_, False)
+    if world > 1:
+        t = torch.tensor([ms, ms_nox], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_nox = [float(x) for x in t.tolist()]
+    if rank == 0:
+        st = cache._state[0]
+        F = Hkv * D
+        Mc = Hkv * w["ncomp"]
+        Mn = F - Mc
+        n_mid_total = cache.curr_tokennum[0]
+        rows_rank0 = st.n_mid
+        # bytes rank 0 streams per step: its slice of the verbatim rows, sinks + window, the replicated coefficients
+        rank_bytes = 2 * (rows_rank0 * 2 * Mn + 2 * (w["S"] + w["W"]) * F) + 4 * w["M"] * 2 * Mc
+        total_bytes = 2 * (n_mid_total * 2 * Mn + 2 * (w["S"] + w["W"]) * F) + 4 * w["M"] * 2 * Mc
+        step_ms = ms / K_
+        peak, peak_src = peaks()
+        line = {"metric": "decode-attn tokens/s", "value": B / (step_ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+                "steps": K_, "warmup": W_, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+                "config": dict(workload_config(args, w), sharding=f"sequence/{world}" if world > 1 else "none",
+                               n_mid=n_mid_total),
+                "gpu_launches": launches, "clocks": clocks,
+                "roofline": {"bound": "hbm", "kernel": {0: "decode_main_kernel", 1: "decode_main_fast_kernel",
+                                                         2: "decode_main_ws2_kernel"}.get(ops.last_decode_path),
+                             "per_gpu_bytes_per_step": rank_bytes, "per_gpu_gbs": rank_bytes / (step_ms * 1e-3) / 1e9,
+                             "achieved": total_bytes / (step_ms * 1e-3) / 1e9, "peak": peak * world, "unit": "GB/s",
+                             "frac": total_bytes / (step_ms * 1e-3) / 1e9 / (peak * world), "traffic": None,
+                             "peak_source": peak_src},
+                "exchange": {"ms_per_step_without": ms_nox / K_, "share_of_step": max(0.0, 1.0 - ms_nox / ms),
+                             "bytes_per_rank_per_step": B * Hq * (D + 2) * 4}}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -452,7 +648,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=16)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "triton"])
+    ap.add_argument("--reference-dir", default=None, help="checkout of the reference, for --impl triton")
     ap.add_argument("--workload", default="llama31_8b_32k", choices=list(WORKLOADS) + ["compress_sweep"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the host-core baseline leg")
     args = ap.parse_args()
@@ -461,6 +658,8 @@ def main():
     w = dict(WORKLOADS[args.workload])
     if args.impl == "reference":
         reference_arm(args, w)
+    elif args.impl == "triton":
+        triton_arm(args, w)
     else:
         ours_arm(args, w)
 

@@ -57,6 +57,7 @@ struct DecodeParams {
   int force_exact;     // debugging / testing aid: never pick the tensor-core pass
   int fast, fNT, fNH;  // tensor-core middle-span pass: column tiles of 8 heads, halves per super-tile
   int wsSEQ, wsNTs;    // warp-specialised form: sequences per CTA, column tiles per sequence
+  int ws2;             // ... with the spectral accumulator in tensor memory (24 warps) instead of registers (16 warps)
   // scratch
   float *w, *cst, *m_part, *l_part, *o_part, *g_part;
   int* err;  // set by a kernel whose bounded wait gave up; the finish kernel then poisons the result
@@ -712,6 +713,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) decode_main_kernel(const __gri
 
 #include "decode_il.cuh"
 #include "decode_ws.cuh"
+#include "decode_ws2.cuh"
 
 constexpr int FAST_THREADS = FAST_T;
 
@@ -736,9 +738,36 @@ __global__ void __launch_bounds__(WS_T, 1) decode_main_ws_kernel(const __grid_co
   if ((int)blockIdx.x < n_il_ctas) {
     const int seq = blockIdx.x / p.n_il_chunks, chunk = blockIdx.x - seq * p.n_il_chunks;
     if (b * p.wsSEQ + seq >= p.a.B) return;
-    il_chunk_mma<T>(p, b * p.wsSEQ + seq, chunk, smem_raw);
+    if (p.TRm == 16)   // wide rows (Hkv*D = 1024): 16-row tiles, the common case, unrolled for exactly one
+      il_chunk_mma<T, 1>(p, b * p.wsSEQ + seq, chunk, smem_raw);
+    else
+      il_chunk_mma<T>(p, b * p.wsSEQ + seq, chunk, smem_raw);
   } else {
     mid_chunk_ws<T>(p, b * p.wsSEQ, blockIdx.x - n_il_ctas, smem_raw);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(W2_T, 1) decode_main_ws2_kernel(const __grid_constant__ DecodeParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const int b = blockIdx.y;
+  const int n_il_ctas = p.wsSEQ * p.n_il_chunks;
+  if ((int)blockIdx.x < n_il_ctas) {
+    // sinks + window rows: a 512-thread pass (its barriers name 512 threads); the other warps hand their
+    // registers to it and leave
+    if (threadIdx.x >= IL_T) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 24;\n");
+      return;
+    }
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;\n");
+    const int seq = blockIdx.x / p.n_il_chunks, chunk = blockIdx.x - seq * p.n_il_chunks;
+    if (b * p.wsSEQ + seq >= p.a.B) return;
+    if (p.TRm == 16)   // wide rows (Hkv*D = 1024): 16-row tiles, the common case, unrolled for exactly one
+      il_chunk_mma<T, 1>(p, b * p.wsSEQ + seq, chunk, smem_raw);
+    else
+      il_chunk_mma<T>(p, b * p.wsSEQ + seq, chunk, smem_raw);
+  } else {
+    mid_chunk_ws2<T>(p, b * p.wsSEQ, blockIdx.x - n_il_ctas, smem_raw);
   }
 }
 
@@ -942,12 +971,13 @@ constexpr int SMEM_LIMIT = 200 * 1024;
 // Switches of the planner.  The one-shot entry points read them from the environment on every call (FA_DECODE_EXACT,
 // FA_DECODE_NO_WS); a layer handle reads them once when it is created.
 struct PlanFlags {
-  bool force_exact, no_ws;
+  bool force_exact, no_ws, ws_tmem;
 };
 static PlanFlags env_flags() {
   PlanFlags f;
   f.force_exact = getenv("FA_DECODE_EXACT") != nullptr;
   f.no_ws = getenv("FA_DECODE_NO_WS") != nullptr;
+  f.ws_tmem = getenv("FA_DECODE_WS_TMEM") != nullptr;   // spectral accumulator in tensor memory (28-warp form)
   return f;
 }
 
@@ -1001,7 +1031,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
   int mid_smem_bytes = 0, il_smem_fast = 0;
   p.J = 8; p.kvh = 1; p.HG = p.R; p.HGp = 8; p.n_groups = 1; p.pitchK = p.pitchV = 16; p.qpitch = 4;
   p.n_mid_chunks = 0; p.mid_chunk = 8;
-  p.fast = 0; p.fNT = 1; p.fNH = 1; p.wsSEQ = 1; p.wsNTs = 1; p.TRm = 16; p.il_tpc = 1;
+  p.fast = 0; p.fNT = 1; p.fNH = 1; p.wsSEQ = 1; p.wsNTs = 1; p.ws2 = 0; p.TRm = 16; p.il_tpc = 1;
   if (a.n_mid > 0) {
     FA_REQUIRE(a.N > 0 && a.T > 0, FA_ERR_SHAPE, "fa_decode_attn: N and T must be positive");
     FA_REQUIRE(a.N <= 1024, FA_ERR_CAPACITY, "fa_decode_attn: N (%d) exceeds 1024", a.N);
@@ -1082,12 +1112,17 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
                            ws_smem(a.N, seq * nbK * 64, seq * nbV * 64).total > 227 * 1024))
           --seq;
         const WsSmem L = ws_smem(a.N, seq * nbK * 64, seq * nbV * 64);
-        if (ok && L.total <= 227 * 1024) {
+        const Ws2Smem L2 = ws2_smem(a.N, seq * nbK * 64, seq * nbV * 64);
+        // the tensor-memory form is opt-in: measured at the Llama-3.1-8B / 32k layer it is 14 % slower than the
+        // form that keeps the accumulator in registers (0.156 ms against 0.137 ms per launch)
+        p.ws2 = (flags.ws_tmem && L2.total <= 227 * 1024) ? 1 : 0;
+        const int need = p.ws2 ? L2.total : L.total;
+        if (ok && need <= 227 * 1024) {
           p.fast = 2;
           p.wsSEQ = seq;
           p.wsNTs = NT;
           p.fNT = seq * NT;
-          mid_smem_bytes = L.total;
+          mid_smem_bytes = need;
         }
       }
     }
@@ -1106,7 +1141,10 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
       const int per_seq = sms / ceil_div(a.B, seqs) > 2 * seqs ? sms / ceil_div(a.B, seqs) : 2 * seqs;
       // a sinks+window tile costs a fixed part (barriers, waits, refill) plus its MMA / softmax work, which
       // grows with rows x KV heads (7.2 K ticks for 16 rows x 8 heads)
-      const double cost_il_tile = 2500.0 + 37.0 * p.TRm * a.Hkv, cost_mid_tok = p.fast == 2 ? 100.0 : 142.0;
+      // (the warp-specialised kernels run 16-row tiles through a pass unrolled for exactly one 16-row block: 5.6 K
+      // ticks per tile at 8 KV heads)
+      const double cost_il_tile = (p.fast == 2 && p.TRm == 16) ? 2000.0 + 28.0 * p.TRm * a.Hkv : 2500.0 + 37.0 * p.TRm * a.Hkv;
+      const double cost_mid_tok = p.fast == 2 ? 100.0 : 142.0;
       const int n_tiles = ceil_div(a.n_sink, p.TRm) + ceil_div(a.n_win, p.TRm);
       double best = 1e30;
       int best_il = 1;
@@ -1189,9 +1227,14 @@ static int launch_decode(const DecodeParams& p, cudaStream_t st) {
   mark(1);
   dim3 g2(p.n_il_chunks + p.n_mid_chunks * p.n_groups, a.B);
   if (p.fast == 2) {
-    if ((rc = set_smem(decode_main_ws_kernel<T>, p.smem_main)) != FA_OK) return rc;
     const dim3 gw(p.wsSEQ * p.n_il_chunks + p.n_mid_chunks, ceil_div(a.B, p.wsSEQ));
-    decode_main_ws_kernel<T><<<gw, WS_T, p.smem_main, st>>>(p);
+    if (p.ws2) {
+      if ((rc = set_smem(decode_main_ws2_kernel<T>, p.smem_main)) != FA_OK) return rc;
+      decode_main_ws2_kernel<T><<<gw, W2_T, p.smem_main, st>>>(p);
+    } else {
+      if ((rc = set_smem(decode_main_ws_kernel<T>, p.smem_main)) != FA_OK) return rc;
+      decode_main_ws_kernel<T><<<gw, WS_T, p.smem_main, st>>>(p);
+    }
   } else if (p.fast) {
 #define FA_FAST_CASE(NT_, NH_)                                                                   \
   if (p.fNT == NT_ && p.fNH == NH_) {                                                            \

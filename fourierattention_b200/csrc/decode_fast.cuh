@@ -96,6 +96,8 @@ __device__ __forceinline__ void mbar_wait(void* bar, uint32_t parity, volatile i
         "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
         : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
     if (ok) return;
+    // back off between looks: a warp that spins at full rate takes issue slots from the warps it is waiting for
+    __nanosleep(40);
     if (*dead || clock64() - t0 > 2000000000LL) {
       *dead = 1;
       atomicExch(err, 1);

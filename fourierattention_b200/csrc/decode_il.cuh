@@ -48,19 +48,23 @@ __host__ __device__ inline IlSmem il_mma_smem(int TR, int F, int Hkv, int D, boo
   return s;
 }
 
+// barrier of the pass's 512 threads (a CTA may carry more warps than the pass uses)
+__device__ __forceinline__ void il_sync() { asm volatile("bar.sync 1, 512;\n" ::: "memory"); }
+
 // byte offset of the 16-byte chunk (row r, columns 8*chunk ..) inside one tensor's part of a stage
 __device__ __forceinline__ int il_sw(int r, int chunk, int box_bytes) {
   return (chunk >> 3) * box_bytes + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
 }
 
 
-// scores + softmax of one KV head over all rows of a tile, by one warp (defined below)
-template <typename T>
+// scores + softmax of one KV head over all rows of a tile, by one warp (defined below); MT = 16-row tiles the
+// code is unrolled for (a tile of rows has at most 16 * MT rows)
+template <typename T, int MT>
 __device__ __forceinline__ void il_scores_softmax(const unsigned char* ks, const T* qb, T* pm, T* pl, float* m_run,
                                                   float* l_run, float* alpha, int g, int D, int mtiles, int valid,
                                                   int qpitch, int ppitch, int box_bytes, float c2, int lane);
 
-template <typename T>
+template <typename T, int MT = IL_MT>
 __device__ void il_chunk_mma(const DecodeParams& p, int b, int chunk, unsigned char* smem) {
   constexpr bool kBf16 = !std::is_same<T, __half>::value;
   const fa_decode_args_t& a = p.a;
@@ -90,7 +94,7 @@ __device__ void il_chunk_mma(const DecodeParams& p, int b, int chunk, unsigned c
     *dead = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  __syncthreads();
+  il_sync();
   // called by a whole warp: request tile t (chunk-relative) into its ring stage
   auto issue = [&](int t) {
     if (t >= nt) return;
@@ -151,14 +155,14 @@ __device__ void il_chunk_mma(const DecodeParams& p, int b, int chunk, unsigned c
     const int row0 = (sink ? gt : gt - n_st) * TR;
     const int valid = min(TR, (sink ? a.n_sink : a.n_win) - row0);
     mbar_wait(full + s, (uint32_t)(t / IL_STAGES) & 1u, dead, p.err);
-    __syncthreads();   // everyone is done with tile t-1: its stage, the probabilities and alpha are free
+    il_sync();   // everyone is done with tile t-1: its stage, the probabilities and alpha are free
     if (warp == IL_W - 1) issue(t + 2);
     const unsigned char* ks = ring + s * L.stage_bytes;
     const unsigned char* vs = ks + L.nbF * box_bytes;
     for (int g = warp; g < Hkv; g += IL_W)
-      il_scores_softmax<T>(ks, qb, pm, pl, m_run, l_run, alpha, g, D, mtiles, valid, qpitch, ppitch, box_bytes, p.c2,
-                           lane);
-    __syncthreads();
+      il_scores_softmax<T, MT>(ks, qb, pm, pl, m_run, l_run, alpha, g, D, mtiles, valid, qpitch, ppitch, box_bytes,
+                               p.c2, lane);
+    il_sync();
     // ---- numerators: unit = (KV head, 16-dim tile) --------------------------------------------------
 #pragma unroll
     for (int i = 0; i < IL_U; ++i) {
@@ -182,7 +186,7 @@ __device__ void il_chunk_mma(const DecodeParams& p, int b, int chunk, unsigned c
       }
     }
   }
-  __syncthreads();
+  il_sync();
 
   const int64_t slot = (int64_t)b * p.NCH + chunk;
   for (int h = tid; h < Hq; h += IL_T) {
@@ -203,16 +207,16 @@ __device__ void il_chunk_mma(const DecodeParams& p, int b, int chunk, unsigned c
   }
 }
 
-template <typename T>
+template <typename T, int MT>
 __device__ __forceinline__ void il_scores_softmax(const unsigned char* ks, const T* qb, T* pm, T* pl, float* m_run,
                                                   float* l_run, float* alpha, int g, int D, int mtiles, int valid,
                                                   int qpitch, int ppitch, int box_bytes, float c2, int lane) {
   constexpr bool kBf16 = !std::is_same<T, __half>::value;
   const int gq = lane >> 2, tq = lane & 3;
   const int dtiles = D / 16;
-  float sc[IL_MT][4];
+  float sc[MT][4];
 #pragma unroll
-  for (int mt = 0; mt < IL_MT; ++mt) {
+  for (int mt = 0; mt < MT; ++mt) {
     if (mt < mtiles) {
       float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       for (int k = 0; k < dtiles; k += 2) {   // two 16-dim steps at a time, two accumulators
@@ -237,7 +241,7 @@ __device__ __forceinline__ void il_scores_softmax(const unsigned char* ks, const
   }
   float mx0 = NEG_BIG, mx1 = NEG_BIG;
 #pragma unroll
-  for (int mt = 0; mt < IL_MT; ++mt) {
+  for (int mt = 0; mt < MT; ++mt) {
     if (mt < mtiles) {
       mx0 = fmaxf(mx0, fmaxf(sc[mt][0], sc[mt][2]));
       mx1 = fmaxf(mx1, fmaxf(sc[mt][1], sc[mt][3]));
@@ -253,7 +257,7 @@ __device__ __forceinline__ void il_scores_softmax(const unsigned char* ks, const
   const float mn0 = fmaxf(mo0, mx0), mn1 = fmaxf(mo1, mx1);
   float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-  for (int mt = 0; mt < IL_MT; ++mt) {
+  for (int mt = 0; mt < MT; ++mt) {
     if (mt < mtiles) {
       const bool ok0 = 16 * mt + gq < valid, ok1 = 16 * mt + gq + 8 < valid;
       const float f0 = ok0 ? __half2float(__float2half_rn(exp2f(sc[mt][0] - mn0))) : 0.f;

@@ -124,7 +124,10 @@ def test_llama_attention_forward_matches_oracle(dtype, P):
             dense_k[i], dense_v[i] = k, v
             ref = dense_ref(q, k, v)
             got = captured[i].cpu().numpy()
-            assert np.abs(got - ref).max() <= 2e-3, ("prefill attention", i, np.abs(got - ref).max())
+            # the module hands o_proj the attention output rounded to the model dtype
+            grid = 2.0 ** (-11 if dtype == "fp16" else -8)
+            err = np.abs(got - ref) - grid * np.abs(ref)
+            assert err.max() <= 2e-3, ("prefill attention", i, err.max())
         # ---- decode --------------------------------------------------------------------------------------
         for s in range(steps):
             out = model(ids[:, P + s:P + s + 1], past_key_values=cache)
