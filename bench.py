@@ -266,6 +266,14 @@ def triton_arm(args, w):
         print(json.dumps(dict(base, unavailable=f"{type(ex).__name__}: {ex}"[:400])), flush=True)
 
 
+def main_kernel_name(path):
+    """Name of the middle-span kernel a decode path runs (fa_decode_path: 0 exact, 1 tensor-core pass, 2 the
+    warp-specialised form, whose tensor-memory variant is opt-in through FA_DECODE_WS_TMEM)."""
+    if path == 2:
+        return "decode_main_ws2_kernel" if os.environ.get("FA_DECODE_WS_TMEM") else "decode_main_ws_kernel"
+    return {0: "decode_main_kernel", 1: "decode_main_fast_kernel"}.get(path)
+
+
 def workload_config(args, w):
     n_mid = w["ctx"] - w["S"] - w["W"]
     return {"workload": args.workload, "layers": w["layers"], "batch": w["B"], "context": w["ctx"],
@@ -437,7 +445,7 @@ def ours_arm(args, w):
         # DRAM read+write bytes of one launch from the committed ncu captures of `profile_small`, whose
         # launches have this workload's per-launch shape (algorithmic bytes 294.1 MB)
         fast = ops.last_decode_path in (1, 2)
-        kernel_name = {0: "decode_main_kernel", 1: "decode_main_fast_kernel", 2: "decode_main_ws_kernel"}[ops.last_decode_path]
+        kernel_name = main_kernel_name(ops.last_decode_path)
         traffic, traffic_src = None, None
         if fast and world == 1 and args.workload in ("llama31_8b_32k", "profile_small"):
             traffic = 307.7e6 if ops.last_decode_path == 2 else 303.7e6
@@ -565,8 +573,7 @@ def seq_split_arm(args, w, world, rank, dev):
                 "config": dict(workload_config(args, w), sharding=f"sequence/{world}" if world > 1 else "none",
                                n_mid=n_mid_total),
                 "gpu_launches": launches, "clocks": clocks,
-                "roofline": {"bound": "hbm", "kernel": {0: "decode_main_kernel", 1: "decode_main_fast_kernel",
-                                                         2: "decode_main_ws2_kernel"}.get(ops.last_decode_path),
+                "roofline": {"bound": "hbm", "kernel": main_kernel_name(ops.last_decode_path),
                              "per_gpu_bytes_per_step": rank_bytes, "per_gpu_gbs": rank_bytes / (step_ms * 1e-3) / 1e9,
                              "achieved": total_bytes / (step_ms * 1e-3) / 1e9, "peak": peak * world, "unit": "GB/s",
                              "frac": total_bytes / (step_ms * 1e-3) / 1e9 / (peak * world), "traffic": None,

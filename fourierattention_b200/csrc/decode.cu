@@ -57,6 +57,8 @@ struct DecodeParams {
   int force_exact;     // debugging / testing aid: never pick the tensor-core pass
   int fast, fNT, fNH;  // tensor-core middle-span pass: column tiles of 8 heads, halves per super-tile
   int wsSEQ, wsNTs;    // warp-specialised form: sequences per CTA, column tiles per sequence
+  int wsGN, wsHG, wsNB;   // ... column tiles per CTA (4 or 2), head groups per sequence, node-basis buffers
+  int wsSlotK, wsSlotV;   // ... columns of a ring slot (whole 64-column boxes of all sequences of the CTA)
   int ws2;             // ... with the spectral accumulator in tensor memory (24 warps) instead of registers (16 warps)
   // scratch
   float *w, *cst, *m_part, *l_part, *o_part, *g_part;
@@ -728,7 +730,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) decode_main_fast_kernel(const
   }
 }
 
-template <typename T>
+template <typename T, int GN>
 __global__ void __launch_bounds__(WS_T, 1) decode_main_ws_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int b = blockIdx.y;
@@ -743,7 +745,8 @@ __global__ void __launch_bounds__(WS_T, 1) decode_main_ws_kernel(const __grid_co
     else
       il_chunk_mma<T>(p, b * p.wsSEQ + seq, chunk, smem_raw);
   } else {
-    mid_chunk_ws<T>(p, b * p.wsSEQ, blockIdx.x - n_il_ctas, smem_raw);
+    const int idx = blockIdx.x - n_il_ctas;   // (chunk, head group)
+    mid_chunk_ws<T, GN>(p, b * p.wsSEQ, idx / p.wsHG, idx % p.wsHG, smem_raw);
   }
 }
 
@@ -1068,6 +1071,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
     p.fast = 0;
     p.wsSEQ = 1;
     p.wsNTs = 1;
+    p.wsGN = 4; p.wsHG = 1; p.wsNB = 2; p.wsSlotK = 64; p.wsSlotV = 64;
     {
       const int NT = ceil_div(a.Hq, 8);
       auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
@@ -1095,8 +1099,11 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
       }
       // warp-specialised form: 128-token super-tiles, and every 8-head column tile must find its
       // verbatim columns inside WS_KS (K) and WS_MTV (V) 16-column tiles, which only the host copies
-      // of the offset tables can tell
-      if (p.fast && NH == 2 && a.kn_h_host && a.vn_h_host && !flags.no_ws) {
+      // of the offset tables can tell.  Up to 2N = 512 coefficient rows a CTA serves four column tiles;
+      // up to 2N = 1024 the heads are divided into groups of 16 (two column tiles per CTA) and a CTA
+      // fetches the verbatim columns of its own KV heads only.
+      const bool ws_shape = a.N % 8 == 0 && a.N <= 512 && NT <= FNT_MAX && a.D % 16 == 0 && il_smem_fast <= 227 * 1024;
+      if (ws_shape && align_ok && NH == 2 && a.kn_h_host && a.vn_h_host && !flags.no_ws && !p.force_exact) {
         bool ok = true;
         for (int nt = 0; nt < NT && ok; ++nt) {
           const int g0 = (8 * nt) / p.R, last = (a.Hq < 8 * nt + 8 ? a.Hq : 8 * nt + 8) - 1, g1 = last / p.R;
@@ -1104,24 +1111,46 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
           const int mtv0 = a.vn_h_host[g0] >> 4, mtvn = ((a.vn_h_host[g1 + 1] + 15) >> 4) - mtv0;
           if ((kc1 - kc0) / 16 > WS_KS || mtvn > WS_MTV) ok = false;
         }
+        const int GN = a.N <= 256 ? 4 : 2;            // column tiles per CTA
+        const int HGn = ceil_div(NT, GN);             // head groups per sequence
+        const int NB = a.N <= 256 ? 2 : 1;            // node-basis buffers
+        // widest run of 64-column boxes a CTA fetches per sequence (its head group's KV heads)
+        int nbK = 0, nbV = 0;
+        for (int hg = 0; hg < HGn; ++hg) {
+          const int hb = hg * 8 * GN, gA = hb / p.R;
+          const int gB = ((a.Hq < hb + 8 * GN ? a.Hq : hb + 8 * GN) - 1) / p.R;
+          const int k0 = a.kn_h_host[gA] & ~63, v0 = a.vn_h_host[gA] & ~63;
+          const int bk = ceil_div(a.kn_h_host[gB + 1] - k0, 64), bv = ceil_div(a.vn_h_host[gB + 1] - v0, 64);
+          if (bk > nbK) nbK = bk;
+          if (bv > nbV) nbV = bv;
+        }
         // sequences per CTA: as many as fill the four column tiles (and the 32 lanes that issue their boxes)
-        int seq = FNT_MAX / NT;
+        int seq = HGn > 1 ? 1 : FNT_MAX / NT;
+        if (GN != 4) seq = 1;
         if (seq > a.B) seq = a.B;
-        const int nbK = ceil_div(a.Mn_k, 64), nbV = ceil_div(a.Mn_v, 64);
         while (seq > 1 && (seq * (nbK > nbV ? nbK : nbV) > 32 ||
-                           ws_smem(a.N, seq * nbK * 64, seq * nbV * 64).total > 227 * 1024))
+                           ws_smem(a.N, seq * nbK * 64, seq * nbV * 64, NB, 8 / GN).total > 227 * 1024))
           --seq;
-        const WsSmem L = ws_smem(a.N, seq * nbK * 64, seq * nbV * 64);
+        const WsSmem L = ws_smem(a.N, seq * nbK * 64, seq * nbV * 64, NB, 8 / GN);
         const Ws2Smem L2 = ws2_smem(a.N, seq * nbK * 64, seq * nbV * 64);
         // the tensor-memory form is opt-in: measured at the Llama-3.1-8B / 32k layer it is 14 % slower than the
         // form that keeps the accumulator in registers (0.156 ms against 0.137 ms per launch)
-        p.ws2 = (flags.ws_tmem && L2.total <= 227 * 1024) ? 1 : 0;
+        p.ws2 = (flags.ws_tmem && GN == 4 && L2.total <= 227 * 1024) ? 1 : 0;
         const int need = p.ws2 ? L2.total : L.total;
-        if (ok && need <= 227 * 1024) {
+        if (ok && need <= 227 * 1024 && (nbK > nbV ? nbK : nbV) <= 32) {
           p.fast = 2;
           p.wsSEQ = seq;
           p.wsNTs = NT;
+          p.wsGN = GN;
+          p.wsHG = HGn;
+          p.wsNB = NB;
+          p.wsSlotK = seq * nbK * 64;
+          p.wsSlotV = seq * nbV * 64;
           p.fNT = seq * NT;
+          p.fNH = 2;
+          p.n_groups = 1; p.kvh = a.Hkv; p.HG = a.Hq;
+          J = 128;
+          p.J = J;
           mid_smem_bytes = need;
         }
       }
@@ -1144,13 +1173,14 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
       // (the warp-specialised kernels run 16-row tiles through a pass unrolled for exactly one 16-row block: 5.6 K
       // ticks per tile at 8 KV heads)
       const double cost_il_tile = (p.fast == 2 && p.TRm == 16) ? 2000.0 + 28.0 * p.TRm * a.Hkv : 2500.0 + 37.0 * p.TRm * a.Hkv;
-      const double cost_mid_tok = p.fast == 2 ? 100.0 : 142.0;
+      const double cost_mid_tok = p.fast == 2 ? (p.wsGN == 2 ? 130.0 : 100.0) : 142.0;
       const int n_tiles = ceil_div(a.n_sink, p.TRm) + ceil_div(a.n_win, p.TRm);
       double best = 1e30;
       int best_il = 1;
+      const int hgs = p.fast == 2 ? p.wsHG : 1;   // CTAs per middle-span chunk (one per head group)
       for (int n_il = 1; n_il < per_seq && n_il <= n_tiles; ++n_il) {
         const int tpc = ceil_div(n_tiles, n_il);
-        int n_mid = per_seq - seqs * ceil_div(n_tiles, tpc);
+        int n_mid = (per_seq - seqs * ceil_div(n_tiles, tpc)) / hgs;
         if (n_mid < 1) break;
         if (n_mid > max_chunks) n_mid = max_chunks;
         const int mid_tok = rup(ceil_div(n_mid_r, n_mid), J);
@@ -1166,7 +1196,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
       p.il_chunk_rows = p.il_tpc * p.TRm;
     }
     int target = ((p.fast ? 1 : 3) * sms) / (a.B * p.n_groups) - p.n_il_chunks;
-    if (p.fast == 2) target = sms / ceil_div(a.B, p.wsSEQ) - p.wsSEQ * p.n_il_chunks;
+    if (p.fast == 2) target = (sms / ceil_div(a.B, p.wsSEQ) - p.wsSEQ * p.n_il_chunks) / p.wsHG;
     if (target < 1) target = 1;
     if (target > max_chunks) target = max_chunks;
     p.mid_chunk = rup(ceil_div(n_mid_r, target), J);
@@ -1227,13 +1257,18 @@ static int launch_decode(const DecodeParams& p, cudaStream_t st) {
   mark(1);
   dim3 g2(p.n_il_chunks + p.n_mid_chunks * p.n_groups, a.B);
   if (p.fast == 2) {
-    const dim3 gw(p.wsSEQ * p.n_il_chunks + p.n_mid_chunks, ceil_div(a.B, p.wsSEQ));
+    const dim3 gw(p.wsSEQ * p.n_il_chunks + p.n_mid_chunks * p.wsHG, ceil_div(a.B, p.wsSEQ));
     if (p.ws2) {
       if ((rc = set_smem(decode_main_ws2_kernel<T>, p.smem_main)) != FA_OK) return rc;
       decode_main_ws2_kernel<T><<<gw, W2_T, p.smem_main, st>>>(p);
     } else {
-      if ((rc = set_smem(decode_main_ws_kernel<T>, p.smem_main)) != FA_OK) return rc;
-      decode_main_ws_kernel<T><<<gw, WS_T, p.smem_main, st>>>(p);
+      if (p.wsGN == 2) {
+        if ((rc = set_smem(decode_main_ws_kernel<T, 2>, p.smem_main)) != FA_OK) return rc;
+        decode_main_ws_kernel<T, 2><<<gw, WS_T, p.smem_main, st>>>(p);
+      } else {
+        if ((rc = set_smem(decode_main_ws_kernel<T, 4>, p.smem_main)) != FA_OK) return rc;
+        decode_main_ws_kernel<T, 4><<<gw, WS_T, p.smem_main, st>>>(p);
+      }
     }
   } else if (p.fast) {
 #define FA_FAST_CASE(NT_, NH_)                                                                   \

@@ -26,6 +26,13 @@
 // batch (their K/V boxes side by side in a ring slot): the node basis and the interpolation weights are the
 // same for all of them, so narrow head counts do not leave score warps idle.
 //
+// Up to 2N = 512 coefficient rows a CTA serves four column tiles (32 heads) and keeps two node-basis buffers, so
+// the spectral warps run ahead.  For 512 < 2N <= 1024 (template parameter GN = 2) the heads of a sequence are
+// divided into groups of 16 that go to different CTAs: a CTA then serves two column tiles, fetches only the
+// verbatim columns of its own KV heads, splits the 2N rows four ways among the spectral warps, gives every score
+// warp eight 16-row tiles of g, and keeps a single node-basis buffer (the accumulators and the w fragments cost
+// the same registers in both forms).
+//
 // The node set is symmetric about the centre of the super-tile, so the basis table holds the eight
 // nodes right of the centre only and the rotation is taken at the centre (a half-integer position:
 // phases are kept modulo 2T).
@@ -43,7 +50,7 @@ struct WsSmem {
   int ec, es, fnt, interp_hi, interp_lo, snode32, snode, pw, ptx, ptp, alpha, mx, lx, bars, slots, total;
   int fpitch, kpad, slot_bytes;
 };
-__host__ __device__ inline WsSmem ws_smem(int N, int Mn_k, int Mn_v) {
+__host__ __device__ inline WsSmem ws_smem(int N, int Mn_k, int Mn_v, int NB = 2, int KP = 2) {
   WsSmem s;
   int o = 0;
   auto take = [&](int bytes) {
@@ -55,10 +62,10 @@ __host__ __device__ inline WsSmem ws_smem(int N, int Mn_k, int Mn_v) {
   s.fpitch = s.kpad + 8;
   s.ec = take(8 * N * 4);
   s.es = take(8 * N * 4);
-  s.fnt = take(2 * 2 * FD * s.fpitch * 2);    // [buffer][hi, lo][node][fpitch]
+  s.fnt = take(NB * 2 * FD * s.fpitch * 2);   // [buffer][hi, lo][node][fpitch]
   s.interp_hi = take(128 * 24 * 2);
   s.interp_lo = take(128 * 24 * 2);
-  s.snode32 = take(2 * FD * 32 * 4);          // partial node scores of the two halves of the 2N rows
+  s.snode32 = take(KP * FD * 32 * 4);         // partial node scores of the KP parts of the 2N rows
   s.snode = take(2 * 2 * 32 * 24 * 2);        // [buffer][hi, lo][head][24]
   s.pw = take(8 * 64 * 8 * 2);                // per score warp: probabilities [64 tokens][8 heads]
   s.ptx = take(2 * 2 * 32 * 24 * 2);          // [buffer][hi, lo][head][24]  probabilities on the nodes
@@ -86,9 +93,11 @@ __device__ __forceinline__ uint32_t pack_pair(T a, T b) {
   return (uint32_t)lo | ((uint32_t)hi << 16);
 }
 
-template <typename T>
-__device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned char* smem) {
+template <typename T, int GN>
+__device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, unsigned char* smem) {
   constexpr int J = 128, HN = 32;
+  constexpr int GI = 16 / GN;   // 16-row tiles of g per score warp
+  constexpr int KP = 8 / GN;    // parts of the 2N rows among the spectral warps of a column tile
   constexpr bool kBf16 = !std::is_same<T, __half>::value;
   const fa_decode_args_t& a = p.a;
   const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
@@ -96,13 +105,15 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
   const int N = a.N, D = a.D, R = p.R, Hq = a.Hq, Mn_k = a.Mn_k, Mn_v = a.Mn_v;
   // A CTA serves `nseq` sequences at once when a sequence has few heads: column tile nt belongs to sequence
   // b0 + nt / NTs and is that sequence's tile nt % NTs; the node basis is the same for all of them.
-  const int NTs = p.wsNTs;
+  const int NB = p.wsNB;                 // node-basis buffers
+  const int hb = hg * 8 * GN;            // first head of this CTA's head group (0 unless the heads are split)
+  const int NTs = p.wsHG > 1 ? min(GN, (Hq - hb + 7) / 8) : p.wsNTs;
   const int nseq = min(p.wsSEQ, a.B - b0);
   const int NT = nseq * NTs;
   const uint32_t T2 = 2u * (uint32_t)a.T;
   const float inv_T = 1.0f / (float)a.T;
   // a ring slot holds the 64-column boxes of all wsSEQ sequences side by side
-  const WsSmem L = ws_smem(N, p.wsSEQ * ((Mn_k + 63) / 64) * 64, p.wsSEQ * ((Mn_v + 63) / 64) * 64);
+  const WsSmem L = ws_smem(N, p.wsSlotK, p.wsSlotV, NB, KP);
   float* ec = reinterpret_cast<float*>(smem + L.ec);
   float* es = reinterpret_cast<float*>(smem + L.es);
   __half* fnt = reinterpret_cast<__half*>(smem + L.fnt);
@@ -129,7 +140,10 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
   const int l1 = min(a.n_mid, l0 + p.mid_chunk);
   const int nst = (l1 - l0 + J - 1) / J;
   const int n_tiles = 4 * nst;   // per super-tile: K half 0, K half 1, V half 0, V half 1
-  const int nbK = (Mn_k + 63) / 64, nbV = (Mn_v + 63) / 64;
+  // verbatim columns of this CTA's KV heads (all of them unless the heads are split): whole 64-column boxes
+  const int gA = hb / R, gB = (min(Hq, hb + 8 * GN) - 1) / R;
+  const int colK0 = a.kn_h[gA] & ~63, colV0 = a.vn_h[gA] & ~63;
+  const int nbK = (a.kn_h[gB + 1] - colK0 + 63) / 64, nbV = (a.vn_h[gB + 1] - colV0 + 63) / 64;
   auto slot_of = [&](int bb) { return (int64_t)bb * p.NCH + p.n_il_chunks + chunk; };
 
   // called by a whole warp: request half tile i into ring slot i % 3
@@ -143,7 +157,8 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
     __syncwarp();
     if (lane < nseq * nb) {   // the boxes of sequence 0, then those of sequence 1, ...
       const int sq = lane / nb, bx = lane - sq * nb;
-      tma_box(slots + s * L.slot_bytes + lane * 8192, is_v ? &p.tm_v : &p.tm_k, 64 * bx, lf, b0 + sq, full_slot + s);
+      tma_box(slots + s * L.slot_bytes + lane * 8192, is_v ? &p.tm_v : &p.tm_k, (is_v ? colV0 : colK0) + 64 * bx, lf,
+              b0 + sq, full_slot + s);
     }
   };
 
@@ -160,7 +175,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
     *dead = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  for (int e = tid; e < 2 * FD * 32; e += WS_T) snode32[e] = 0.f;
+  for (int e = tid; e < KP * FD * 32; e += WS_T) snode32[e] = 0.f;
   __syncthreads();
   if (wp == 8) {
     if (lane == 0) {
@@ -190,22 +205,23 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
   if (wp < 8) {
     // =========================== spectral warps ================================================
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(WS_SREG));
-    const int nt1 = wp & 3, khalf = wp >> 2;
+    const int nt1 = wp % GN, khalf = wp / GN;   // column tile and part of the 2N rows of this warp
     // this chunk's verbatim-V partial starts from zero (the score warps add into it at the end)
     {
+      const int nh = p.wsHG > 1 ? min(Hq - hb, 8 * GN) : Hq;   // heads this CTA writes
       for (int sq = 0; sq < nseq; ++sq) {
-        float* ob = p.o_part + slot_of(b0 + sq) * Hq * D;
-        for (int e = tid; e < Hq * D; e += 256) ob[e] = 0.f;
+        float* ob = p.o_part + (slot_of(b0 + sq) * Hq + hb) * D;
+        for (int e = tid; e < nh * D; e += 256) ob[e] = 0.f;
       }
     }
     // w as persistent B fragments (hi / lo): k = frequency row, n = head; this warp holds column
     // tile nt1 for half `khalf` of the 2N rows
     constexpr int KH = 16;
-    const int kh_steps = (ktot + 1) / 2;
+    const int kh_steps = (ktot + KP - 1) / KP;
     uint32_t bhi[KH][2], blo[KH][2];
     {
       const float* wb = p.w + (int64_t)(b0 + nt1 / NTs) * Hq * 2 * N;
-      const int h = 8 * (nt1 % NTs) + gq;
+      const int h = hb + 8 * (nt1 % NTs) + gq;
 #pragma unroll
       for (int i = 0; i < KH; ++i) {
         const int k0 = 16 * (khalf * kh_steps + i);
@@ -227,28 +243,35 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
       }
     }
     // phases (modulo 2T) of this thread's two frequencies at the centre of the first super-tile
-    const int np = tid & 127, kk = tid >> 7;
-    uint32_t ph2[2], d2[2];
+    // (a thread serves the frequency pairs np0, np0 + 128: the second one exists for N > 256 only)
+    constexpr int NIT = GN == 4 ? 1 : 2;
+    const int np0 = tid & 127, kk = tid >> 7;
+    uint32_t ph2[NIT][2], d2[NIT][2];
 #pragma unroll
-    for (int f = 0; f < 2; ++f) {
-      const uint32_t n = (uint32_t)(2 * np + f);
-      const uint64_t centre2 = 2ull * ((uint64_t)a.mid_l0 + (uint64_t)l0) + (uint64_t)(J - 1);
-      ph2[f] = phase_mod(centre2 % (uint64_t)T2, n, T2);
-      d2[f] = phase_mod((uint64_t)(2 * J), n, T2);
-    }
+    for (int it = 0; it < NIT; ++it)
+#pragma unroll
+      for (int f = 0; f < 2; ++f) {
+        const uint32_t n = (uint32_t)(2 * (np0 + 128 * it) + f);
+        const uint64_t centre2 = 2ull * ((uint64_t)a.mid_l0 + (uint64_t)l0) + (uint64_t)(J - 1);
+        ph2[it][f] = phase_mod(centre2 % (uint64_t)T2, n, T2);
+        d2[it][f] = phase_mod((uint64_t)(2 * J), n, T2);
+      }
     for (int j = 0; j < nst; ++j) {
-      const int buf = j & 1;
-      __half* fh = fnt + (buf * 2 + 0) * FD * fpitch;
-      __half* fl = fnt + (buf * 2 + 1) * FD * fpitch;
-      if (j >= 2) mbar_wait(empty_sp + buf, ((j >> 1) - 1) & 1, dead, p.err);
+      const int buf = j & 1, fb = j % NB;
+      __half* fh = fnt + (fb * 2 + 0) * FD * fpitch;
+      __half* fl = fnt + (fb * 2 + 1) * FD * fpitch;
+      if (j >= NB) mbar_wait(empty_sp + fb, ((j / NB) - 1) & 1, dead, p.err);
       // ---- node basis: rotate the table to this super-tile's centre ------------------------------
-      if (2 * np < N) {
+#pragma unroll
+      for (int it = 0; it < NIT; ++it) {
+        const int np = np0 + 128 * it;
+        if (2 * np >= N) break;
         float rc[2], rs[2];
 #pragma unroll
         for (int f = 0; f < 2; ++f) {
-          sincospif((float)ph2[f] * inv_T, &rs[f], &rc[f]);
-          ph2[f] += d2[f];
-          if (ph2[f] >= T2) ph2[f] -= T2;
+          sincospif((float)ph2[it][f] * inv_T, &rs[f], &rc[f]);
+          ph2[it][f] += d2[it][f];
+          if (ph2[it][f] >= T2) ph2[it][f] -= T2;
         }
         auto put = [&](int k, float c0, float c1, float s0, float s1) {
           const __half2 ch = __floats2half2_rn(c0, c1), sh = __floats2half2_rn(s0, s1);
@@ -293,7 +316,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
             mma16816<__half>(acc[3 * (i & 1) + 2], ah, blo[i]);
           }
         }
-        float* red = snode32 + khalf * (FD * HN);
+        float* red = snode32 + khalf * (FD * HN);   // this part's partial sums
         const int col = 8 * nt1 + 2 * tq;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -308,13 +331,16 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
         for (int e = tid; e < FD * HN; e += 256) {
           const int k = e / HN, h = e - k * HN;
           __half hi, lo;
-          split_h(snode32[e] + snode32[FD * HN + e], hi, lo);
+          float v = snode32[e];
+#pragma unroll
+          for (int kp = 1; kp < KP; ++kp) v += snode32[kp * FD * HN + e];
+          split_h(v, hi, lo);
           sh_[h * 24 + k] = hi;
           sl_[h * 24 + k] = lo;
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(full_sp + buf);
+      if (lane == 0) mbar_arrive(full_sp + fb);
     }
     __syncthreads();
     return;
@@ -332,7 +358,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
   // column ranges of this warp's heads in the verbatim stores
   int kc0 = 0, kc1 = 0, mtv0 = 0, mtvn = 0;
   if (act) {
-    const int g0 = (8 * ntl) / R, g1 = (min(Hq, 8 * ntl + 8) - 1) / R;
+    const int g0 = (hb + 8 * ntl) / R, g1 = (min(Hq, hb + 8 * ntl + 8) - 1) / R;
     kc0 = a.kn_h[g0] & ~15;
     kc1 = (a.kn_h[g1 + 1] + 15) & ~15;
     mtv0 = a.vn_h[g0] >> 4;
@@ -344,7 +370,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
   uint32_t bq[WS_KS][2];
   {
     const T* q = reinterpret_cast<const T*>(a.q) + (int64_t)bb * a.q_sb;
-    const int h = 8 * ntl + gq;
+    const int h = hb + 8 * ntl + gq;
     const int g = h / R;
     int c_lo = 0, c_hi = 0;
     if (act && h < Hq) {
@@ -364,17 +390,17 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
     }
   }
   const int hc0 = 8 * nt + 2 * tq;    // this thread's two columns among the CTA's 32
-  const int hl0 = 8 * ntl + 2 * tq;   // ... and the heads of sequence bb they stand for
+  const int hl0 = hb + 8 * ntl + 2 * tq;   // ... and the heads of sequence bb they stand for
   const float cst0 = (act && hl0 < Hq) ? p.cst[(int64_t)bb * Hq + hl0] : 0.f;
   const float cst1 = (act && hl0 + 1 < Hq) ? p.cst[(int64_t)bb * Hq + hl0 + 1] : 0.f;
   // first column of this sequence's boxes inside a K / V ring slot
-  const int cbK = sq * nbK * 64, cbV = sq * nbV * 64;
+  const int cbK = sq * nbK * 64 - colK0, cbV = sq * nbV * 64 - colV0;   // absolute column -> column inside a ring slot
   float m_run0 = NEG_BIG, m_run1 = NEG_BIG, lsum0 = 0.f, lsum1 = 0.f;
-  float Gacc[4][4][4];
+  float Gacc[GI][GN][4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < GI; ++i)
 #pragma unroll
-    for (int n = 0; n < 4; ++n)
+    for (int n = 0; n < GN; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) Gacc[i][n][e] = 0.f;
   float Oacc[WS_MTV][4];
@@ -384,10 +410,10 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
     for (int e = 0; e < 4; ++e) Oacc[i][e] = 0.f;
 
   for (int st = 0; st < nst; ++st) {
-    const int buf = st & 1;
+    const int buf = st & 1, fb = st % NB;
     const int tok0 = l0 + st * J + half * FH;   // first token of this warp's half
-    const __half* fh = fnt + (buf * 2 + 0) * FD * fpitch;
-    const __half* fl = fnt + (buf * 2 + 1) * FD * fpitch;
+    const __half* fh = fnt + (fb * 2 + 0) * FD * fpitch;
+    const __half* fl = fnt + (fb * 2 + 1) * FD * fpitch;
     float sc[4][4];
 #pragma unroll
     for (int mt = 0; mt < 4; ++mt)
@@ -426,7 +452,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
       mbar_wait(empty_slot + sK, parK, dead, p.err);
       issue_tile(iK + 3);
     }
-    mbar_wait(full_sp + buf, (st >> 1) & 1, dead, p.err);
+    mbar_wait(full_sp + fb, (st / NB) & 1, dead, p.err);
     if (act) {
       // ---- add the node scores interpolated to this warp's 64 tokens ---------------------------------
       uint32_t bh[2], bl[2];
@@ -620,10 +646,10 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
     ws_group_sync(7);
     // ---- g[2N x HN] += Fn_t^T[2N x 16] * pt[16 x HN]  (this warp's 16-row tiles) -------------------
     {
-      uint32_t bf[4][2], bl[4][2];
-      float ap[4][2];
+      uint32_t bf[GN][2], bl[GN][2];
+      float ap[GN][2];
 #pragma unroll
-      for (int n = 0; n < 4; ++n) {
+      for (int n = 0; n < GN; ++n) {
         if (n < NT) {
           const int o = (8 * n + lds_b_row(lane)) * 24 + lds_b_col(lane);
           ldsm_x2(bf[n], ptx + (buf * 2 + 0) * 32 * 24 + o);
@@ -633,7 +659,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
         }
       }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < GI; ++i) {
         const int mt = qw + 8 * i;
         if (mt < ktot) {
           uint32_t ah[4], al_[4];
@@ -641,7 +667,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
           ldsm_x4_t(ah, fh + off);
           ldsm_x4_t(al_, fl + off);
 #pragma unroll
-          for (int n = 0; n < 4; ++n) {
+          for (int n = 0; n < GN; ++n) {
             if (n < NT) {
               Gacc[i][n][0] *= ap[n][0];
               Gacc[i][n][1] *= ap[n][1];
@@ -650,19 +676,19 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
             }
           }
 #pragma unroll
-          for (int n = 0; n < 4; ++n)
+          for (int n = 0; n < GN; ++n)
             if (n < NT) mma16816<__half>(Gacc[i][n], al_, bf[n]);
 #pragma unroll
-          for (int n = 0; n < 4; ++n)
+          for (int n = 0; n < GN; ++n)
             if (n < NT) mma16816<__half>(Gacc[i][n], ah, bl[n]);
 #pragma unroll
-          for (int n = 0; n < 4; ++n)
+          for (int n = 0; n < GN; ++n)
             if (n < NT) mma16816<__half>(Gacc[i][n], ah, bf[n]);
         }
       }
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(empty_sp + buf);
+    if (lane == 0) mbar_arrive(empty_sp + fb);
   }
 
   // ---- chunk partials ---------------------------------------------------------------------------
@@ -706,18 +732,18 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, unsigned 
     }
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < GI; ++i) {
     const int mt = qw + 8 * i;
     if (mt < ktot) {
 #pragma unroll
-      for (int n = 0; n < 4; ++n) {
+      for (int n = 0; n < GN; ++n) {
         if (n < NT) {
           const int sqn = n / NTs, ntn = n - sqn * NTs;   // sequence and tile-within-sequence of column tile n
           float* gb = p.g_part + (((int64_t)(b0 + sqn) * p.n_mid_chunks + chunk) * Hq) * 2 * N;
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int row = 16 * mt + gq + 8 * (e >> 1);
-            const int h = 8 * ntn + 2 * tq + (e & 1);
+            const int h = hb + 8 * ntn + 2 * tq + (e & 1);
             if (row < 2 * N && h < Hq) gb[(int64_t)h * 2 * N + row] = Gacc[i][n][e];
           }
         }

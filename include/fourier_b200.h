@@ -183,13 +183,18 @@ typedef struct {
 /* Bytes of scratch fa_decode_attn needs for this geometry (only the size fields are read). */
 size_t fa_decode_scratch_bytes(const fa_decode_args_t* args_host);
 /* Which middle-span pass fa_decode_attn will run for these arguments (sizes, strides and pointer
- * alignment are read): 1 = tensor-core pass (the spectral score is evaluated at 16 nodes per 64/128-token
- * super-tile and interpolated; needs N % 8 == 0, N <= 256, Hq <= 32, Mn_* <= 256, 16-byte aligned verbatim
- * rows and at most 1.5 turns of the highest frequency per super-tile), 2 = the same mathematics with the
- * warps of a CTA specialised and pipelined (additionally needs 128-token super-tiles, kn_h_host / vn_h_host,
- * and per 8 query heads at most 64 verbatim-K and 64 verbatim-V columns after rounding to 16), 0 = exact
- * CUDA-core pass, negative = fa_status_t.  The environment variable FA_DECODE_EXACT forces 0,
- * FA_DECODE_NO_WS keeps 2 from being chosen. */
+ * alignment are read):
+ *   2 = warp-specialised tensor-core pass: the spectral score is evaluated at 16 nodes per 128-token super-tile
+ *       and interpolated.  Needs N % 8 == 0, N <= 512, Hq <= 32, head_dim % 16 == 0, 16-byte aligned verbatim rows,
+ *       at most 1.5 turns of the highest frequency per super-tile (128 (N - 1) <= 1.5 T), kn_h_host / vn_h_host,
+ *       and per 8 query heads at most 64 verbatim-K and 64 verbatim-V columns after rounding to 16.  Above
+ *       N = 256 the heads of a sequence are served in groups of 16 by different CTAs.
+ *   1 = the same mathematics phase by phase (all warps together): N <= 256, Mn_* <= 256, 64- or 128-token
+ *       super-tiles, no host tables needed.
+ *   0 = exact CUDA-core pass (any shape).
+ *   negative = fa_status_t.
+ * Environment: FA_DECODE_EXACT forces 0, FA_DECODE_NO_WS keeps 2 from being chosen, FA_DECODE_WS_TMEM selects
+ * the variant of 2 that keeps the spectral accumulator in tensor memory (tcgen05; N <= 256). */
 int fa_decode_path(const fa_decode_args_t* args_host);
 int fa_decode_attn(const fa_decode_args_t* args_host, fa_stream_t stream);
 
@@ -212,7 +217,9 @@ int fa_decode_attn(const fa_decode_args_t* args_host, fa_stream_t stream);
  *  - All calls on a device share the one array and it keeps whatever the last call left there.  Nothing
  *    has to be cleared between calls: every word a call reads was written earlier in that same call.  Two
  *    calls that overlap on the GPU (different streams, or graphs replayed concurrently) race on it; keep
- *    calls of this entry point ordered on one stream per device. */
+ *    calls of this entry point ordered on one stream per device.
+ *  - The looked-up address is kept per device for the life of the process; do not use this entry point
+ *    across a cudaDeviceReset of that device. */
 #define FA_DECODE_STATIC_SCRATCH_BYTES (24u << 20)
 int fa_decode_attn_static(const fa_decode_args_t* args_host, fa_stream_t stream);
 

@@ -47,13 +47,20 @@ FAST_CASES = {
     # few heads per sequence: a CTA of the warp-specialised kernel takes four (then one) / two sequences
     "fast_packed_4seq": _geom(B=5, Hq=8, Hkv=2, D=64, S=4, W=40, M=16, P=900, dtype="bf16", ncomp=40, seed=209),
     "fast_packed_2seq": _geom(B=3, Hq=16, Hkv=4, D=64, S=2, W=24, M=32, P=1500, ncomp=48, seed=210),
+    # M = 1024 (the reference's default): 2N = 1024 coefficient rows, the heads of a sequence go to two CTAs
+    "fast_m1024_head_groups": _geom(B=1, Hq=32, Hkv=8, D=128, S=4, W=64, M=1024, P=46000, dtype="bf16", ncomp=96, seed=211),
+    # ... with three column tiles (the second head group holds one) and two sequences
+    "fast_m1024_three_tiles": _geom(B=2, Hq=24, Hkv=8, D=128, S=4, W=40, M=1024, P=45000, ncomp=120, seed=212),
 }
 
 
 # of these, the shapes the warp-specialised form takes (128-token super-tiles, at most 64 verbatim K and V
 # columns per 8 query heads)
 WS_CASES = {"fast_gqa4_bf16", "fast_32heads_fp16", "fast_one_kv_head", "fast_nothing_verbatim",
-            "fast_nothing_compressed", "fast_llama8b_layer", "fast_packed_4seq", "fast_packed_2seq"}
+            "fast_nothing_compressed", "fast_llama8b_layer", "fast_packed_4seq", "fast_packed_2seq",
+            "fast_m1024_head_groups", "fast_m1024_three_tiles"}
+# of those, the shapes only the warp-specialised form takes (more than 512 coefficient rows)
+WS_ONLY_CASES = {"fast_m1024_head_groups", "fast_m1024_three_tiles"}
 
 
 @pytest.mark.parametrize("name", list(FAST_CASES))
@@ -79,7 +86,7 @@ def test_decode_attn_tensor_core_pass(name, monkeypatch):
     if ops.last_decode_path == 2:
         monkeypatch.setenv("FA_DECODE_NO_WS", "1")
         out = ops.decode_attn(qd, num_head_q=g["Hq"], num_head_kv=g["Hkv"], T=oc.T, **inp)
-        assert ops.last_decode_path == 1, "shape was expected to take the tensor-core pass"
+        assert ops.last_decode_path == (0 if name in WS_ONLY_CASES else 1), "shape was expected to take the tensor-core pass"
         check_tensor_core_result(out)
     monkeypatch.setenv("FA_DECODE_EXACT", "1")
     exact = ops.decode_attn(qd, num_head_q=g["Hq"], num_head_kv=g["Hkv"], T=oc.T, **inp)
