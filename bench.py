@@ -266,6 +266,35 @@ def triton_arm(args, w):
         print(json.dumps(dict(base, unavailable=f"{type(ex).__name__}: {ex}"[:400])), flush=True)
 
 
+KERNEL_SOURCES = ("decode.cu", "decode_fast.cuh", "decode_il.cuh", "decode_ws.cuh", "decode_ws2.cuh", "common.cuh")
+
+
+def kernel_source_sha16():
+    """Digest of the decode kernel sources: a recorded DRAM-traffic figure is only quoted while the sources it was
+    measured on are unchanged."""
+    import hashlib
+    h = hashlib.sha256()
+    for name in KERNEL_SOURCES:
+        with open(os.path.join(ROOT, "fourierattention_b200", "csrc", name), "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()[:16]
+
+
+def recorded_traffic(kernel_name, workload):
+    """DRAM read + write bytes of one launch of ``kernel_name`` from the ncu capture summarised under profiles/
+    (``<kernel>.traffic.json``, written next to the summary it was read from).  Returns (bytes or None, note)."""
+    path = os.path.join(ROOT, "profiles", f"{kernel_name}.traffic.json")
+    if not os.path.exists(path):
+        return None, "no ncu capture recorded for this kernel"
+    with open(path) as f:
+        rec = json.load(f).get(workload)
+    if rec is None:
+        return None, "no ncu capture recorded for this workload"
+    if rec.get("source_sha16") != kernel_source_sha16():
+        return None, f"the kernel sources changed since the capture of {rec.get('captured')}: figure withheld"
+    return float(rec["dram_bytes"]), rec.get("source", "")
+
+
 def main_kernel_name(path):
     """Name of the middle-span kernel a decode path runs (fa_decode_path: 0 exact, 1 tensor-core pass, 2 the
     warp-specialised form, whose tensor-memory variant is opt-in through FA_DECODE_WS_TMEM)."""
@@ -446,11 +475,13 @@ def ours_arm(args, w):
         # launches have this workload's per-launch shape (algorithmic bytes 294.1 MB)
         fast = ops.last_decode_path in (1, 2)
         kernel_name = main_kernel_name(ops.last_decode_path)
+        # DRAM bytes of one launch as ncu measured them on `profile_small`, whose launches have this workload's
+        # per-launch shape; scaled by the share of the KV heads a rank holds (traffic grows with the row width)
         traffic, traffic_src = None, None
-        if fast and world == 1 and args.workload in ("llama31_8b_32k", "profile_small"):
-            traffic = 307.7e6 if ops.last_decode_path == 2 else 303.7e6
-            traffic_src = "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch of profile_small " \
-                          f"(profiles/{kernel_name}.profile_small.md)"
+        if args.workload in ("llama31_8b_32k", "profile_small"):
+            traffic, traffic_src = recorded_traffic(kernel_name, "profile_small")
+            if traffic is not None:
+                traffic *= frac_heads
         h2d = L * B * (hq_l * D + 2 * hk * D) * 2
         d2h = L * B * hq_l * D * 4
         line = {
@@ -587,7 +618,7 @@ def seq_split_arm(args, w, world, rank, dev):
 
 
 def compress_sweep(args):
-    """BASELINE config 4: the prefill projection alone, bf16, one layer, 8 KV heads x 128 dims of which 96 per
+    """The prefill projection alone (the compression sweep configuration): bf16, one layer, 8 KV heads x 128 dims of which 96 per
     head are compressed (Mc = 768), K/V ~ N(0,1) x per-dim scale ~ LogUniform(0.1, 10); spans 4096..131072,
     M in {256, 512, 1024}.  Prints one JSON line with TFLOP/s (algorithmic FLOPs 2*M*K*Mc of the compressed
     columns only) against the measured bf16 tensor peak, and the coefficient error against a float64
@@ -640,8 +671,15 @@ def compress_sweep(args):
             got_s = coef[0][N + n][:, pos].double()
             err = max(float((got_c - ref_c).abs().max()), float((got_s - ref_s).abs().max()))
             rms = float(torch.cat([ref_c, ref_s]).pow(2).mean().sqrt())
+            # the reference's own projection of the same columns: complex64 FFT of length T_c, first N bins
+            # (fourier_triton_valid4_v2.py:857-865); its error against float64 is the floor the contract is defined on
+            fq = torch.fft.fft(x[0][:, cols].to(torch.complex64), n=T_c, dim=0)[:N][n]
+            fft_c, fft_s = fq.real.double(), -fq.imag.double()
+            fft_err = max(float((fft_c - ref_c).abs().max()), float((fft_s - ref_s).abs().max()))
+            vs_fft = max(float((got_c - fft_c).abs().max()), float((got_s - fft_s).abs().max()))
             rows.append({"span": span, "M": M, "ms": ms, "tflops": flops / ms / 1e9, "frac_of_peak": flops / ms / 1e9 / peak,
-                         "max_abs_err": err, "coef_rms": rms, "rel_err": err / rms, "T": T, "T_c": T_c})
+                         "max_abs_err": err, "coef_rms": rms, "rel_err": err / rms, "T": T, "T_c": T_c,
+                         "reference_fft_max_abs_err": fft_err, "max_abs_diff_to_reference_fft": vs_fft})
     print(json.dumps({"metric": "compression TFLOP/s (algorithmic)", "unit": "TFLOP/s", "n_gpus": 1, "dtype": "bf16",
                       "data": "synthetic", "config": {"workload": "compress_sweep", "Mc": Mc, "source_columns": F},
                       "roofline": {"bound": "tensor", "peak": peak, "unit": "TFLOP/s",
@@ -659,7 +697,11 @@ def main():
     ap.add_argument("--reference-dir", default=None, help="checkout of the reference, for --impl triton")
     ap.add_argument("--workload", default="llama31_8b_32k", choices=list(WORKLOADS) + ["compress_sweep"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the host-core baseline leg")
+    ap.add_argument("--print-source-sha", action="store_true", help="print the digest of the decode kernel sources")
     args = ap.parse_args()
+    if args.print_source_sha:
+        print(kernel_source_sha16())
+        return
     if args.workload == "compress_sweep":
         return compress_sweep(args)
     w = dict(WORKLOADS[args.workload])

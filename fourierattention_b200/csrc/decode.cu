@@ -59,6 +59,7 @@ struct DecodeParams {
   int wsSEQ, wsNTs;    // warp-specialised form: sequences per CTA, column tiles per sequence
   int wsGN, wsHG, wsNB;   // ... column tiles per CTA (4 or 2), head groups per sequence, node-basis buffers
   int wsSlotK, wsSlotV;   // ... columns of a ring slot (whole 64-column boxes of all sequences of the CTA)
+  int wsHPT, wsKS;        // ... query heads per column tile (8, or 6 for three per KV head), 16-column steps per tile
   int ws2;             // ... with the spectral accumulator in tensor memory (24 warps) instead of registers (16 warps)
   // scratch
   float *w, *cst, *m_part, *l_part, *o_part, *g_part;
@@ -730,7 +731,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) decode_main_fast_kernel(const
   }
 }
 
-template <typename T, int GN>
+template <typename T, int GN, int KS>
 __global__ void __launch_bounds__(WS_T, 1) decode_main_ws_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int b = blockIdx.y;
@@ -746,7 +747,7 @@ __global__ void __launch_bounds__(WS_T, 1) decode_main_ws_kernel(const __grid_co
       il_chunk_mma<T>(p, b * p.wsSEQ + seq, chunk, smem_raw);
   } else {
     const int idx = blockIdx.x - n_il_ctas;   // (chunk, head group)
-    mid_chunk_ws<T, GN>(p, b * p.wsSEQ, idx / p.wsHG, idx % p.wsHG, smem_raw);
+    mid_chunk_ws<T, GN, KS>(p, b * p.wsSEQ, idx / p.wsHG, idx % p.wsHG, smem_raw);
   }
 }
 
@@ -1071,7 +1072,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
     p.fast = 0;
     p.wsSEQ = 1;
     p.wsNTs = 1;
-    p.wsGN = 4; p.wsHG = 1; p.wsNB = 2; p.wsSlotK = 64; p.wsSlotV = 64;
+    p.wsGN = 4; p.wsHG = 1; p.wsNB = 2; p.wsSlotK = 64; p.wsSlotV = 64; p.wsHPT = 8; p.wsKS = 4;
     {
       const int NT = ceil_div(a.Hq, 8);
       auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
@@ -1102,23 +1103,31 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
       // of the offset tables can tell.  Up to 2N = 512 coefficient rows a CTA serves four column tiles;
       // up to 2N = 1024 the heads are divided into groups of 16 (two column tiles per CTA) and a CTA
       // fetches the verbatim columns of its own KV heads only.
-      const bool ws_shape = a.N % 8 == 0 && a.N <= 512 && NT <= FNT_MAX && a.D % 16 == 0 && il_smem_fast <= 227 * 1024;
+      // heads per column tile: 8, or the largest multiple of the GQA ratio below 8 when 8 is not one (a tile then
+      // never cuts the query heads of a KV head in two)
+      const int HPT = (p.R >= 8 || 8 % p.R == 0) ? 8 : (8 / p.R) * p.R;
+      const int NTw = ceil_div(a.Hq, HPT);
+      const bool ws_shape = a.N % 8 == 0 && a.N <= 512 && NTw <= FNT_MAX && a.D % 16 == 0 && il_smem_fast <= 227 * 1024;
       if (ws_shape && align_ok && NH == 2 && a.kn_h_host && a.vn_h_host && !flags.no_ws && !p.force_exact) {
-        bool ok = true;
-        for (int nt = 0; nt < NT && ok; ++nt) {
-          const int g0 = (8 * nt) / p.R, last = (a.Hq < 8 * nt + 8 ? a.Hq : 8 * nt + 8) - 1, g1 = last / p.R;
+        const int NT = NTw;
+        int steps = 1;   // most 16-column steps a tile needs for its verbatim K or V columns
+        for (int nt = 0; nt < NT; ++nt) {
+          const int g0 = (HPT * nt) / p.R, last = (a.Hq < HPT * nt + HPT ? a.Hq : HPT * nt + HPT) - 1, g1 = last / p.R;
           const int kc0 = a.kn_h_host[g0] & ~15, kc1 = (a.kn_h_host[g1 + 1] + 15) & ~15;
           const int mtv0 = a.vn_h_host[g0] >> 4, mtvn = ((a.vn_h_host[g1 + 1] + 15) >> 4) - mtv0;
-          if ((kc1 - kc0) / 16 > WS_KS || mtvn > WS_MTV) ok = false;
+          if ((kc1 - kc0) / 16 > steps) steps = (kc1 - kc0) / 16;
+          if (mtvn > steps) steps = mtvn;
         }
+        const bool ok = steps <= WS_KS_MAX;
+        const int KS = (steps <= 4 && HPT == 8) ? 4 : 8;   // the KS = 4 instances are compiled for 8 heads per tile
         const int GN = a.N <= 256 ? 4 : 2;            // column tiles per CTA
         const int HGn = ceil_div(NT, GN);             // head groups per sequence
         const int NB = a.N <= 256 ? 2 : 1;            // node-basis buffers
         // widest run of 64-column boxes a CTA fetches per sequence (its head group's KV heads)
         int nbK = 0, nbV = 0;
         for (int hg = 0; hg < HGn; ++hg) {
-          const int hb = hg * 8 * GN, gA = hb / p.R;
-          const int gB = ((a.Hq < hb + 8 * GN ? a.Hq : hb + 8 * GN) - 1) / p.R;
+          const int hb = hg * HPT * GN, gA = hb / p.R;
+          const int gB = ((a.Hq < hb + HPT * GN ? a.Hq : hb + HPT * GN) - 1) / p.R;
           const int k0 = a.kn_h_host[gA] & ~63, v0 = a.vn_h_host[gA] & ~63;
           const int bk = ceil_div(a.kn_h_host[gB + 1] - k0, 64), bv = ceil_div(a.vn_h_host[gB + 1] - v0, 64);
           if (bk > nbK) nbK = bk;
@@ -1135,7 +1144,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
         const Ws2Smem L2 = ws2_smem(a.N, seq * nbK * 64, seq * nbV * 64);
         // the tensor-memory form is opt-in: measured at the Llama-3.1-8B / 32k layer it is 14 % slower than the
         // form that keeps the accumulator in registers (0.156 ms against 0.137 ms per launch)
-        p.ws2 = (flags.ws_tmem && GN == 4 && L2.total <= 227 * 1024) ? 1 : 0;
+        p.ws2 = (flags.ws_tmem && GN == 4 && HPT == 8 && KS == 4 && L2.total <= 227 * 1024) ? 1 : 0;
         const int need = p.ws2 ? L2.total : L.total;
         if (ok && need <= 227 * 1024 && (nbK > nbV ? nbK : nbV) <= 32) {
           p.fast = 2;
@@ -1146,6 +1155,8 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
           p.wsNB = NB;
           p.wsSlotK = seq * nbK * 64;
           p.wsSlotV = seq * nbV * 64;
+          p.wsHPT = HPT;
+          p.wsKS = KS;
           p.fNT = seq * NT;
           p.fNH = 2;
           p.n_groups = 1; p.kvh = a.Hkv; p.HG = a.Hq;
@@ -1262,13 +1273,13 @@ static int launch_decode(const DecodeParams& p, cudaStream_t st) {
       if ((rc = set_smem(decode_main_ws2_kernel<T>, p.smem_main)) != FA_OK) return rc;
       decode_main_ws2_kernel<T><<<gw, W2_T, p.smem_main, st>>>(p);
     } else {
-      if (p.wsGN == 2) {
-        if ((rc = set_smem(decode_main_ws_kernel<T, 2>, p.smem_main)) != FA_OK) return rc;
-        decode_main_ws_kernel<T, 2><<<gw, WS_T, p.smem_main, st>>>(p);
-      } else {
-        if ((rc = set_smem(decode_main_ws_kernel<T, 4>, p.smem_main)) != FA_OK) return rc;
-        decode_main_ws_kernel<T, 4><<<gw, WS_T, p.smem_main, st>>>(p);
-      }
+#define FA_WS_CASE(GN_, KS_)                                                                 \
+  if (p.wsGN == GN_ && p.wsKS == KS_) {                                                       \
+    if ((rc = set_smem(decode_main_ws_kernel<T, GN_, KS_>, p.smem_main)) != FA_OK) return rc; \
+    decode_main_ws_kernel<T, GN_, KS_><<<gw, WS_T, p.smem_main, st>>>(p);                     \
+  }
+      FA_WS_CASE(4, 4) FA_WS_CASE(4, 8) FA_WS_CASE(2, 4) FA_WS_CASE(2, 8)
+#undef FA_WS_CASE
     }
   } else if (p.fast) {
 #define FA_FAST_CASE(NT_, NH_)                                                                   \

@@ -38,8 +38,8 @@
 // phases are kept modulo 2T).
 #pragma once
 
-constexpr int WS_MTV = 4;   // 16-column tiles of verbatim V a score warp owns
-constexpr int WS_KS = 4;    // 16-column steps of verbatim K a score warp contracts
+constexpr int WS_KS_MAX = 8;   // most 16-column steps of verbatim K (and 16-column tiles of verbatim V) a score warp
+                               // handles (template parameter KS: 4 or 8)
 constexpr int WS_T = 512;
 constexpr int WS_SREG = 56, WS_QREG = 200;   // registers per thread of the two groups (sum = 2 x 128): the
 // score warps must not spill (with 222 KB of shared memory the L1 that would catch spills is tiny), the spectral
@@ -93,8 +93,9 @@ __device__ __forceinline__ uint32_t pack_pair(T a, T b) {
   return (uint32_t)lo | ((uint32_t)hi << 16);
 }
 
-template <typename T, int GN>
+template <typename T, int GN, int KS>
 __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, unsigned char* smem) {
+  constexpr int MTV = KS;       // 16-column tiles of verbatim V a score warp owns
   constexpr int J = 128, HN = 32;
   constexpr int GI = 16 / GN;   // 16-row tiles of g per score warp
   constexpr int KP = 8 / GN;    // parts of the 2N rows among the spectral warps of a column tile
@@ -106,8 +107,12 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
   // A CTA serves `nseq` sequences at once when a sequence has few heads: column tile nt belongs to sequence
   // b0 + nt / NTs and is that sequence's tile nt % NTs; the node basis is the same for all of them.
   const int NB = p.wsNB;                 // node-basis buffers
-  const int hb = hg * 8 * GN;            // first head of this CTA's head group (0 unless the heads are split)
-  const int NTs = p.wsHG > 1 ? min(GN, (Hq - hb + 7) / 8) : p.wsNTs;
+  // A column tile holds HPT heads (8, or the largest multiple of the GQA ratio below 8 so that a tile never cuts
+  // a KV head's query heads in two: 6 for three query heads per KV head); columns HPT..7 of a tile are padding.
+  // (the KS = 4 instances are compiled for HPT = 8, so that the common shapes pay nothing for the general case)
+  const int HPT = KS == 4 ? 8 : p.wsHPT;
+  const int hb = hg * HPT * GN;          // first head of this CTA's head group (0 unless the heads are split)
+  const int NTs = p.wsHG > 1 ? min(GN, (Hq - hb + HPT - 1) / HPT) : p.wsNTs;
   const int nseq = min(p.wsSEQ, a.B - b0);
   const int NT = nseq * NTs;
   const uint32_t T2 = 2u * (uint32_t)a.T;
@@ -141,7 +146,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
   const int nst = (l1 - l0 + J - 1) / J;
   const int n_tiles = 4 * nst;   // per super-tile: K half 0, K half 1, V half 0, V half 1
   // verbatim columns of this CTA's KV heads (all of them unless the heads are split): whole 64-column boxes
-  const int gA = hb / R, gB = (min(Hq, hb + 8 * GN) - 1) / R;
+  const int gA = hb / R, gB = (min(Hq, hb + HPT * GN) - 1) / R;
   const int colK0 = a.kn_h[gA] & ~63, colV0 = a.vn_h[gA] & ~63;
   const int nbK = (a.kn_h[gB + 1] - colK0 + 63) / 64, nbV = (a.vn_h[gB + 1] - colV0 + 63) / 64;
   auto slot_of = [&](int bb) { return (int64_t)bb * p.NCH + p.n_il_chunks + chunk; };
@@ -208,7 +213,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
     const int nt1 = wp % GN, khalf = wp / GN;   // column tile and part of the 2N rows of this warp
     // this chunk's verbatim-V partial starts from zero (the score warps add into it at the end)
     {
-      const int nh = p.wsHG > 1 ? min(Hq - hb, 8 * GN) : Hq;   // heads this CTA writes
+      const int nh = p.wsHG > 1 ? min(Hq - hb, HPT * GN) : Hq;   // heads this CTA writes
       for (int sq = 0; sq < nseq; ++sq) {
         float* ob = p.o_part + (slot_of(b0 + sq) * Hq + hb) * D;
         for (int e = tid; e < nh * D; e += 256) ob[e] = 0.f;
@@ -221,7 +226,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
     uint32_t bhi[KH][2], blo[KH][2];
     {
       const float* wb = p.w + (int64_t)(b0 + nt1 / NTs) * Hq * 2 * N;
-      const int h = hb + 8 * (nt1 % NTs) + gq;
+      const int h = gq < HPT ? hb + HPT * (nt1 % NTs) + gq : Hq;   // padding columns: no head
 #pragma unroll
       for (int i = 0; i < KH; ++i) {
         const int k0 = 16 * (khalf * kh_steps + i);
@@ -358,7 +363,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
   // column ranges of this warp's heads in the verbatim stores
   int kc0 = 0, kc1 = 0, mtv0 = 0, mtvn = 0;
   if (act) {
-    const int g0 = (hb + 8 * ntl) / R, g1 = (min(Hq, hb + 8 * ntl + 8) - 1) / R;
+    const int g0 = (hb + HPT * ntl) / R, g1 = (min(Hq, hb + HPT * ntl + HPT) - 1) / R;
     kc0 = a.kn_h[g0] & ~15;
     kc1 = (a.kn_h[g1 + 1] + 15) & ~15;
     mtv0 = a.vn_h[g0] >> 4;
@@ -367,10 +372,10 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
   const int nks = (kc1 - kc0) >> 4;   // 16-column steps of the verbatim-K contraction
   // the heads' verbatim-K query entries as MMA B fragments (raw model-dtype values; the softmax
   // scale is applied to the fp32 sums)
-  uint32_t bq[WS_KS][2];
+  uint32_t bq[KS][2];
   {
     const T* q = reinterpret_cast<const T*>(a.q) + (int64_t)bb * a.q_sb;
-    const int h = hb + 8 * ntl + gq;
+    const int h = gq < HPT ? hb + HPT * ntl + gq : Hq;   // padding columns: no head
     const int g = h / R;
     int c_lo = 0, c_hi = 0;
     if (act && h < Hq) {
@@ -378,7 +383,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
       c_hi = a.kn_h[g + 1];
     }
 #pragma unroll
-    for (int ks = 0; ks < WS_KS; ++ks) {
+    for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         const int col = kc0 + 16 * ks + 2 * tq + 8 * r;
@@ -390,9 +395,10 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
     }
   }
   const int hc0 = 8 * nt + 2 * tq;    // this thread's two columns among the CTA's 32
-  const int hl0 = hb + 8 * ntl + 2 * tq;   // ... and the heads of sequence bb they stand for
-  const float cst0 = (act && hl0 < Hq) ? p.cst[(int64_t)bb * Hq + hl0] : 0.f;
-  const float cst1 = (act && hl0 + 1 < Hq) ? p.cst[(int64_t)bb * Hq + hl0 + 1] : 0.f;
+  const int hl0 = hb + HPT * ntl + 2 * tq;   // ... and the heads of sequence bb they stand for
+  const bool hv0 = act && 2 * tq < HPT && hl0 < Hq, hv1 = act && 2 * tq + 1 < HPT && hl0 + 1 < Hq;   // real heads?
+  const float cst0 = hv0 ? p.cst[(int64_t)bb * Hq + hl0] : 0.f;
+  const float cst1 = hv1 ? p.cst[(int64_t)bb * Hq + hl0 + 1] : 0.f;
   // first column of this sequence's boxes inside a K / V ring slot
   const int cbK = sq * nbK * 64 - colK0, cbV = sq * nbV * 64 - colV0;   // absolute column -> column inside a ring slot
   float m_run0 = NEG_BIG, m_run1 = NEG_BIG, lsum0 = 0.f, lsum1 = 0.f;
@@ -403,9 +409,9 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
     for (int n = 0; n < GN; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) Gacc[i][n][e] = 0.f;
-  float Oacc[WS_MTV][4];
+  float Oacc[MTV][4];
 #pragma unroll
-  for (int i = 0; i < WS_MTV; ++i)
+  for (int i = 0; i < MTV; ++i)
 #pragma unroll
     for (int e = 0; e < 4; ++e) Oacc[i][e] = 0.f;
 
@@ -428,7 +434,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
       mbar_wait(full_slot + sK, parK, dead, p.err);
       const unsigned char* ks_ = slots + sK * L.slot_bytes;
 #pragma unroll
-      for (int ks = 0; ks < WS_KS; ++ks) {
+      for (int ks = 0; ks < KS; ++ks) {
         if (ks < nks) {
 #pragma unroll
           for (int mt = 0; mt < 4; ++mt) {
@@ -589,7 +595,7 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
       mbar_wait(full_slot + sV, parV, dead, p.err);
       const unsigned char* vs_ = slots + sV * L.slot_bytes;
 #pragma unroll
-      for (int i = 0; i < WS_MTV; ++i) {
+      for (int i = 0; i < MTV; ++i) {
         Oacc[i][0] *= al0;
         Oacc[i][1] *= al1;
         Oacc[i][2] *= al0;
@@ -597,18 +603,21 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
       }
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
-        uint32_t af[WS_MTV][4];
 #pragma unroll
-        for (int i = 0; i < WS_MTV; ++i)
-          if (i < mtvn)
-            ldsm_x4_t(af[i], vs_ + sw_off(16 * ks + lds_at_row(lane), (cbV + 16 * (mtv0 + i) + lds_at_col(lane)) >> 3));
+        for (int i0 = 0; i0 < MTV; i0 += 4) {   // four V tiles at a time: their fragments are in flight together
+          uint32_t af[4][4];
 #pragma unroll
-        for (int i = 0; i < WS_MTV; ++i)
-          if (i < mtvn) mma16816<T>(Oacc[i], af[i], bp[ks]);
-        if (kBf16) {
+          for (int i = 0; i < 4; ++i)
+            if (i0 + i < mtvn)
+              ldsm_x4_t(af[i], vs_ + sw_off(16 * ks + lds_at_row(lane), (cbV + 16 * (mtv0 + i0 + i) + lds_at_col(lane)) >> 3));
 #pragma unroll
-          for (int i = 0; i < WS_MTV; ++i)
-            if (i < mtvn) mma16816<T>(Oacc[i], af[i], bp_lo[ks]);
+          for (int i = 0; i < 4; ++i)
+            if (i0 + i < mtvn) mma16816<T>(Oacc[i0 + i], af[i], bp[ks]);
+          if (kBf16) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (i0 + i < mtvn) mma16816<T>(Oacc[i0 + i], af[i], bp_lo[ks]);
+          }
         }
       }
       __syncwarp();
@@ -704,11 +713,11 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
   __syncthreads();   // the spectral warps have zeroed this chunk's verbatim-V partial
   if (act && half == 0 && gq == 0) {
     const int64_t slot_id = slot_of(bb);
-    if (hl0 < Hq) {
+    if (hv0) {
       p.m_part[slot_id * Hq + hl0] = m_run0;
       p.l_part[slot_id * Hq + hl0] = lsum0 + lx[nt * 8 + 2 * tq];
     }
-    if (hl0 + 1 < Hq) {
+    if (hv1) {
       p.m_part[slot_id * Hq + hl0 + 1] = m_run1;
       p.l_part[slot_id * Hq + hl0 + 1] = lsum1 + lx[nt * 8 + 2 * tq + 1];
     }
@@ -717,13 +726,13 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
     // both halves add their numerators (two addends onto zero: the order does not change the sum)
     float* ob = p.o_part + slot_of(bb) * Hq * D;
 #pragma unroll
-    for (int i = 0; i < WS_MTV; ++i) {
+    for (int i = 0; i < MTV; ++i) {
       if (i < mtvn) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int c = 16 * (mtv0 + i) + gq + 8 * (e >> 1);
           const int h = hl0 + (e & 1);
-          if (c < Mn_v && h < Hq) {
+          if (c < Mn_v && ((e & 1) ? hv1 : hv0)) {
             const int g = h / R;
             if (c >= a.vn_h[g] && c < a.vn_h[g + 1]) atomicAdd(ob + h * D + a.vn_list[c] - g * D, Oacc[i][e]);
           }
@@ -743,8 +752,8 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int row = 16 * mt + gq + 8 * (e >> 1);
-            const int h = hb + 8 * ntn + 2 * tq + (e & 1);
-            if (row < 2 * N && h < Hq) gb[(int64_t)h * 2 * N + row] = Gacc[i][n][e];
+            const int h = hb + HPT * ntn + 2 * tq + (e & 1);
+            if (row < 2 * N && 2 * tq + (e & 1) < HPT && h < Hq) gb[(int64_t)h * 2 * N + row] = Gacc[i][n][e];
           }
         }
       }
