@@ -60,6 +60,7 @@ struct DecodeParams {
   int wsGN, wsHG, wsNB;   // ... column tiles per CTA (4 or 2), head groups per sequence, node-basis buffers
   int wsSlotK, wsSlotV;   // ... columns of a ring slot (whole 64-column boxes of all sequences of the CTA)
   int wsHPT, wsKS;        // ... query heads per column tile (8, or 6 for three per KV head), 16-column steps per tile
+  int w_frag;          // prepare writes w as fp16 hi + lo in MMA-fragment order (warp-specialised kernels) instead of fp32 rows
   int ws2;             // ... with the spectral accumulator in tensor memory (24 warps) instead of registers (16 warps)
   // scratch
   float *w, *cst, *m_part, *l_part, *o_part, *g_part;
@@ -161,9 +162,25 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_prepare_kernel(const __gri
       }
     }
     const float wscale = p.c2 / (float)N;
+    if (p.w_frag) {
+      // fp16 hi + lo in the order the spectral warps load their m16n8k16 B fragments: per head, 16 bytes per
+      // (16-row step, lane quad position tq) = {hi rows 2tq,2tq+1 | hi rows 2tq+8,+9 | lo ... | lo ...}
+      const int ks = row >> 4, j = row & 15, rr = j >> 3, tq = (j & 7) >> 1, odd = j & 1;
 #pragma unroll
-    for (int r = 0; r < R_MAX; ++r)
-      if (r < R) p.w[((int64_t)b * a.Hq + g * R + r) * 2 * N + row] = acc[r] * wscale;
+      for (int r = 0; r < R_MAX; ++r) {
+        if (r < R) {
+          const float v = acc[r] * wscale;
+          const __half hi = __float2half_rn(v), lo = __float2half_rn(v - __half2float(hi));
+          __half* dst = reinterpret_cast<__half*>(p.w) + (((int64_t)b * a.Hq + g * R + r) * (2 * N / 16) + ks) * 32 + tq * 8;
+          dst[rr * 2 + odd] = hi;
+          dst[4 + rr * 2 + odd] = lo;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < R_MAX; ++r)
+        if (r < R) p.w[((int64_t)b * a.Hq + g * R + r) * 2 * N + row] = acc[r] * wscale;
+    }
   }
   if (blockIdx.x == 0 && g == 0 && b == 0 && tid == 0) *p.err = 0;
   if (blockIdx.x == 0 && warp < R) {
@@ -1035,7 +1052,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
   int mid_smem_bytes = 0, il_smem_fast = 0;
   p.J = 8; p.kvh = 1; p.HG = p.R; p.HGp = 8; p.n_groups = 1; p.pitchK = p.pitchV = 16; p.qpitch = 4;
   p.n_mid_chunks = 0; p.mid_chunk = 8;
-  p.fast = 0; p.fNT = 1; p.fNH = 1; p.wsSEQ = 1; p.wsNTs = 1; p.ws2 = 0; p.TRm = 16; p.il_tpc = 1;
+  p.fast = 0; p.fNT = 1; p.fNH = 1; p.wsSEQ = 1; p.wsNTs = 1; p.ws2 = 0; p.w_frag = 0; p.TRm = 16; p.il_tpc = 1;
   if (a.n_mid > 0) {
     FA_REQUIRE(a.N > 0 && a.T > 0, FA_ERR_SHAPE, "fa_decode_attn: N and T must be positive");
     FA_REQUIRE(a.N <= 1024, FA_ERR_CAPACITY, "fa_decode_attn: N (%d) exceeds 1024", a.N);
@@ -1148,6 +1165,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
         const int need = p.ws2 ? L2.total : L.total;
         if (ok && need <= 227 * 1024 && (nbK > nbV ? nbK : nbV) <= 32) {
           p.fast = 2;
+          p.w_frag = 1;
           p.wsSEQ = seq;
           p.wsNTs = NT;
           p.wsGN = GN;

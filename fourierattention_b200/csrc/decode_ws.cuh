@@ -219,32 +219,23 @@ __device__ void mid_chunk_ws(const DecodeParams& p, int b0, int chunk, int hg, u
         for (int e = tid; e < nh * D; e += 256) ob[e] = 0.f;
       }
     }
-    // w as persistent B fragments (hi / lo): k = frequency row, n = head; this warp holds column
-    // tile nt1 for half `khalf` of the 2N rows
+    // w as persistent B fragments (hi / lo): k = coefficient row, n = head; this warp holds column tile nt1 for part
+    // `khalf` of the 2N rows.  The prepare kernel has written them in fragment order: one 16-byte load per step.
     constexpr int KH = 16;
     const int kh_steps = (ktot + KP - 1) / KP;
     uint32_t bhi[KH][2], blo[KH][2];
     {
-      const float* wb = p.w + (int64_t)(b0 + nt1 / NTs) * Hq * 2 * N;
-      const int h = gq < HPT ? hb + HPT * (nt1 % NTs) + gq : Hq;   // padding columns: no head
+      const int h = gq < HPT ? hb + HPT * (nt1 % NTs) + gq : Hq   /* padding columns: no head */;
+      const uint4* wf = reinterpret_cast<const uint4*>(p.w) + ((int64_t)(b0 + nt1 / NTs) * Hq + h) * (2 * N / 16) * 4 + tq;
 #pragma unroll
       for (int i = 0; i < KH; ++i) {
-        const int k0 = 16 * (khalf * kh_steps + i);
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          const int k = k0 + 2 * tq + 8 * r;
-          float v0 = 0.f, v1 = 0.f;
-          if (nt1 < NT && i < kh_steps && h < Hq && k < 2 * N) {
-            v0 = wb[(int64_t)h * 2 * N + k];
-            v1 = wb[(int64_t)h * 2 * N + k + 1];
-          }
-          __half h0, l0_, h1, l1_;
-          split_h(v0, h0, l0_);
-          split_h(v1, h1, l1_);
-          __half2 hh = __halves2half2(h0, h1), ll = __halves2half2(l0_, l1_);
-          bhi[i][r] = *reinterpret_cast<uint32_t*>(&hh);
-          blo[i][r] = *reinterpret_cast<uint32_t*>(&ll);
-        }
+        const int ks = khalf * kh_steps + i;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (nt1 < NT && i < kh_steps && h < Hq && ks < ktot) v = __ldg(wf + ks * 4);
+        bhi[i][0] = v.x;
+        bhi[i][1] = v.y;
+        blo[i][0] = v.z;
+        blo[i][1] = v.w;
       }
     }
     // phases (modulo 2T) of this thread's two frequencies at the centre of the first super-tile
