@@ -326,9 +326,9 @@ def recorded_traffic(kernel_name, workload):
 
 def main_kernel_name(path):
     """Name of the middle-span kernel a decode path runs (fa_decode_path: 0 exact, 1 tensor-core pass, 2 the
-    warp-specialised form, whose tensor-memory variant is opt-in through FA_DECODE_WS_TMEM)."""
-    if path == 2:
-        return "decode_main_ws2_kernel" if os.environ.get("FA_DECODE_WS_TMEM") else "decode_main_ws_kernel"
+    warp-specialised form, 3 its variant with the spectral accumulator in tensor memory)."""
+    if path in (2, 3):
+        return "decode_main_ws2_kernel" if path == 3 else "decode_main_ws_kernel"
     return {0: "decode_main_kernel", 1: "decode_main_fast_kernel"}.get(path)
 
 
@@ -502,7 +502,7 @@ def ours_arm(args, w):
         step_bytes = op_bytes * B * L
         # DRAM read+write bytes of one launch from the committed ncu captures of `profile_small`, whose
         # launches have this workload's per-launch shape (algorithmic bytes 294.1 MB)
-        fast = ops.last_decode_path in (1, 2)
+        fast = ops.last_decode_path in (1, 2, 3)
         kernel_name = main_kernel_name(ops.last_decode_path)
         # DRAM bytes of one launch as ncu measured them on `profile_small`, whose launches have this workload's
         # per-launch shape; scaled by the share of the KV heads a rank holds (traffic grows with the row width)

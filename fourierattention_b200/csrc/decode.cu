@@ -61,10 +61,12 @@ struct DecodeParams {
   int wsSlotK, wsSlotV;   // ... columns of a ring slot (whole 64-column boxes of all sequences of the CTA)
   int wsHPT, wsKS;        // ... query heads per column tile (8, or 6 for three per KV head), 16-column steps per tile
   int w_frag;          // prepare writes w as fp16 hi + lo in MMA-fragment order (warp-specialised kernels) instead of fp32 rows
-  int ws2;             // ... with the spectral accumulator in tensor memory (24 warps) instead of registers (16 warps)
+  int ws2;             // ... with the spectral accumulator in tensor memory (tcgen05 g update, 20 warps) instead of registers (16 warps)
   // scratch
   float *w, *cst, *m_part, *l_part, *o_part, *g_part;
   int* err;  // set by a kernel whose bounded wait gave up; the finish kernel then poisons the result
+  float* tab;   // tensor-memory variant: node-offset rotation table and interpolation matrix as the main kernel's
+                // shared-memory images (written by the prepare kernel: they depend on N and T only)
   int64_t scratch_floats;
 };
 
@@ -115,6 +117,11 @@ __host__ __device__ inline int il_smem_bytes(int TR, int F, int Hq, int Hqp, int
 // grid (blocks of 256 coefficient rows, KV head, sequence); a thread owns one row of one KV head and
 // walks the head's contiguous column segment with 128-bit loads, every load independent of the others
 // ---------------------------------------------------------------------------------------------
+// floats of the table block of the tensor-memory variant: cos / sin of the 8 node offsets for N frequencies,
+// then the 128 x 16 interpolation matrix as fp16 hi and lo terms with rows of 24
+__host__ __device__ inline int ws2_table_floats(int N) { return 16 * N + 2 * 128 * 24 / 2; }
+__device__ void ws2_write_tables(const DecodeParams& p, int idx, int stride);   // defined with the kernel that reads them
+
 template <typename T>
 __global__ void __launch_bounds__(DEC_THREADS) decode_prepare_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -183,6 +190,8 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_prepare_kernel(const __gri
     }
   }
   if (blockIdx.x == 0 && g == 0 && b == 0 && tid == 0) *p.err = 0;
+  if (p.ws2)   // spread over the whole grid: at most a few entries per thread
+    ws2_write_tables(p, ((b * gridDim.y + g) * gridDim.x + blockIdx.x) * DEC_THREADS + tid, gridDim.x * gridDim.y * gridDim.z * DEC_THREADS);
   if (blockIdx.x == 0 && warp < R) {
     const int h = g * R + warp;
     float acc = 0.f;
@@ -735,6 +744,31 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) decode_main_kernel(const __gri
 #include "decode_ws.cuh"
 #include "decode_ws2.cuh"
 
+// (called by the prepare kernel) entry e of the node-offset table: node 8+k lies (2 x_k - 127) / 2 tokens right of a
+// super-tile's centre; the interpolation matrix is split into fp16 hi + lo
+__device__ void ws2_write_tables(const DecodeParams& p, int idx, int stride) {
+  const int N = p.a.N;
+  const uint32_t T2 = 2u * (uint32_t)p.a.T;
+  const float inv_T = 1.0f / (float)p.a.T;
+  for (int e = idx; e < 8 * N; e += stride) {
+    const int k = e / N, n = e - k * N;
+    const uint32_t ph = phase_mod((uint64_t)(2 * c_nodes128[8 + k] - 127), (uint32_t)n, T2);
+    float sn, cs;
+    sincospif((float)ph * inv_T, &sn, &cs);
+    p.tab[e] = cs;
+    p.tab[8 * N + e] = sn;
+  }
+  __half* ih = reinterpret_cast<__half*>(p.tab + 16 * N);
+  __half* il = ih + 128 * 24;
+  for (int e = idx; e < 128 * 24; e += stride) {
+    const int j = e / 24, k = e - j * 24;
+    __half hi = __float2half_rn(0.f), lo = hi;
+    if (k < FD) split_h(g_interp128[j * FD + k], hi, lo);
+    ih[e] = hi;
+    il[e] = lo;
+  }
+}
+
 constexpr int FAST_THREADS = FAST_T;
 
 template <typename T, int NT, int NH>
@@ -780,7 +814,7 @@ __global__ void __launch_bounds__(W2_T, 1) decode_main_ws2_kernel(const __grid_c
       asm volatile("setmaxnreg.dec.sync.aligned.u32 24;\n");
       return;
     }
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;\n");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 112;\n");
     const int seq = blockIdx.x / p.n_il_chunks, chunk = blockIdx.x - seq * p.n_il_chunks;
     if (b * p.wsSEQ + seq >= p.a.B) return;
     if (p.TRm == 16)   // wide rows (Hkv*D = 1024): 16-row tiles, the common case, unrolled for exactly one
@@ -990,7 +1024,7 @@ __global__ void merge_kernel(const float* __restrict__ o, const float* __restric
 constexpr int SMEM_LIMIT = 200 * 1024;
 
 // Switches of the planner.  The one-shot entry points read them from the environment on every call (FA_DECODE_EXACT,
-// FA_DECODE_NO_WS); a layer handle reads them once when it is created.
+// FA_DECODE_NO_WS, FA_DECODE_NO_TMEM); a layer handle reads them once when it is created.
 struct PlanFlags {
   bool force_exact, no_ws, ws_tmem;
 };
@@ -998,7 +1032,7 @@ static PlanFlags env_flags() {
   PlanFlags f;
   f.force_exact = getenv("FA_DECODE_EXACT") != nullptr;
   f.no_ws = getenv("FA_DECODE_NO_WS") != nullptr;
-  f.ws_tmem = getenv("FA_DECODE_WS_TMEM") != nullptr;   // spectral accumulator in tensor memory (28-warp form)
+  f.ws_tmem = getenv("FA_DECODE_NO_TMEM") == nullptr;   // spectral accumulator in tensor memory where the shape allows
   return f;
 }
 
@@ -1015,10 +1049,12 @@ static void bind_scratch(DecodeParams& p, void* scratch) {
   const int64_t ow = take(B * Hq * 2 * a.N), oc = take(B * Hq), om = take(B * p.NCH * Hq), ol = take(B * p.NCH * Hq);
   const int64_t oo = take(B * p.NCH * Hq * a.D), og = take(B * p.n_mid_chunks * Hq * 2 * a.N);
   const int64_t oe = take(4);
+  const int64_t ot = take(p.ws2 ? ws2_table_floats(a.N) : 0);
   p.scratch_floats = o;
   float* s = reinterpret_cast<float*>(scratch);
   p.w = s + ow; p.cst = s + oc; p.m_part = s + om; p.l_part = s + ol; p.o_part = s + oo; p.g_part = s + og;
   p.err = reinterpret_cast<int*>(s + oe);
+  p.tab = s + ot;
 }
 
 static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags& flags) {
@@ -1159,9 +1195,10 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
           --seq;
         const WsSmem L = ws_smem(a.N, seq * nbK * 64, seq * nbV * 64, NB, 8 / GN);
         const Ws2Smem L2 = ws2_smem(a.N, seq * nbK * 64, seq * nbV * 64);
-        // the tensor-memory form is opt-in: measured at the Llama-3.1-8B / 32k layer it is 14 % slower than the
-        // form that keeps the accumulator in registers (0.156 ms against 0.137 ms per launch)
-        p.ws2 = (flags.ws_tmem && GN == 4 && HPT == 8 && KS == 4 && L2.total <= 227 * 1024) ? 1 : 0;
+        // the tensor-memory form where it applies: measured at the Llama-3.1-8B / 32k layer it takes 0.114 ms per launch
+        // against 0.133 ms of the form that keeps the accumulator in registers
+        p.ws2 = (flags.ws_tmem && GN == 4 && HPT == 8 && KS == 4 && a.Mn_k <= W2_IDX && a.Mn_v <= W2_IDX && a.Hkv < 40 &&
+                 L2.total <= 227 * 1024) ? 1 : 0;
         const int need = p.ws2 ? L2.total : L.total;
         if (ok && need <= 227 * 1024 && (nbK > nbV ? nbK : nbV) <= 32) {
           p.fast = 2;
@@ -1372,7 +1409,7 @@ extern "C" int fa_decode_path(const fa_decode_args_t* args) {
   a.scratch = nullptr;
   int rc = make_plan(a, p, env_flags());
   if (rc != FA_OK) return rc;
-  return a.n_mid > 0 ? p.fast : 0;
+  return a.n_mid > 0 ? (p.fast == 2 && p.ws2 ? 3 : p.fast) : 0;
 }
 
 // Pointer / alignment checks of a planned call (p.a holds the caller's arguments, scratch already bound).
@@ -1571,7 +1608,7 @@ static int layer_plan(fa_layer* L, int Hq, int n_mid, float sm_scale) {
   L->plan_Hq = Hq;
   L->plan_hi = n_mid > 0 ? rup(n_mid, p.J) : 0;
   L->plan_lo = n_mid > 0 ? L->plan_hi - p.J : -1;
-  L->last_path = n_mid > 0 ? p.fast : 0;
+  L->last_path = n_mid > 0 ? (p.fast == 2 && p.ws2 ? 3 : p.fast) : 0;
   return FA_OK;
 }
 

@@ -2,47 +2,53 @@
 // after decode_ws.cuh (same namespace; same ldmatrix / mma.sync / mbarrier / TMA helpers and the same
 // mathematics as decode_fast.cuh: node interpolation of the band-limited spectral score).
 //
-// 28 warps per CTA (7 warp groups; registers are handed out per group of four warps):
+// 20 warps per CTA (5 warp groups; registers are handed out per group of four warps):
 //
 //   spectral warps (0..7)    node basis of super-tile j (rotation of a fixed table to the super-tile's centre),
 //                            written in the core-matrix layout that both ldmatrix and the tcgen05 descriptors
 //                            read, and the node scores s_node = Fn_j * w as mma.sync GEMMs (w stays in
 //                            registers); they run up to two super-tiles ahead
-//   score warps (8..23)      warp = (8-head column tile nt, 32-token quarter qt): verbatim-K scores,
-//                            interpolation of the node scores, softmax, projection of the probabilities onto
-//                            the nodes, verbatim-V numerators.  The four warps of a column tile are one warp
-//                            group; they exchange the tile's maximum and the projected probabilities through
-//                            shared memory and a 128-thread named barrier.
-//   service warps (24, 25)   everything that is a hand-off rather than arithmetic: warp 24 refills the ring of K / V
-//                            half tiles (TMA boxes) as the score warps release the slots; warp 25 waits until the four
-//                            quarters of every tile have delivered their projected probabilities, adds them up,
-//                            writes them as the B operand and issues the g update on the tensor cores.  (Warps 26 and
-//                            27 only complete the warp group.)
+//   score warps (8..15)      warp = (8-head column tile nt, 64-token half): verbatim-K scores, interpolation of
+//                            the node scores, softmax, projection of the probabilities onto the nodes,
+//                            verbatim-V numerators.  The two warps of a column tile exchange the tile's maximum
+//                            through shared memory and a 64-thread named barrier; they never meet other tiles.
+//   service warps (16..19)   everything that is a hand-off rather than arithmetic.  Warp 16 refills the ring of
+//                            K / V half tiles (TMA boxes) as the score warps release the slots; warp 17 waits
+//                            until both halves of every tile have delivered their projected probabilities, adds
+//                            them up, writes them as the B operand and issues the g update on the tensor cores.
+//                            All four own one lane quadrant of tensor memory each: together they rescale a
+//                            tile's accumulators when its running maximum moves, and at the end they stage g in
+//                            shared memory for the bulk copies that write it out.
 //
-// The spectral accumulator g[2N x 8 heads] of a column tile lives in tensor memory (4 blocks of 128 rows x 16
-// columns): after the four quarters have been added up, a service warp issues
-//     g += Fn_j^T[2N x 16 nodes] * pt[16 nodes x 8 heads]
-// as tcgen05.mma (M = 128, N = 16 with 8 padding columns, K = 16; basis and pt as fp16 hi + lo pairs, three
-// products) and commits it to the mbarrier that hands the basis buffer back to the spectral warps.  No score
-// warp waits for that GEMM, the accumulator costs no registers, and the score warps never meet across tiles.
+// The spectral accumulator g[2N x 32 head columns] of the four column tiles lives in tensor memory (4 blocks of
+// 128 rows x 32 columns): after the halves have been added up, warp 17 issues
+//     g += Fn_j^T[2N x 16 nodes] * pt[16 nodes x 32 head columns]
+// as tcgen05.mma (M = 128, N = 32, K = 16; basis and pt as fp16 hi + lo pairs, three products per row block)
+// and commits it to the mbarrier that hands the basis buffer back to the spectral warps.  No score
+// warp waits for that GEMM or touches tensor memory, and the accumulator costs no registers.
 //
 // Accumulators in tensor memory cannot be rescaled for free, so the running maximum is lazy: it moves only when
-// a super-tile's maximum exceeds it by more than 2^6, and only then are the tile's accumulators rescaled (its
-// four warps read their lane quadrants, multiply and write back).  Probabilities are at most 2^6 and stay inside
-// fp16; all sums use the same reference maximum, which is what the chunk reports.
+// a super-tile's maximum exceeds it by more than 2^6.  The score warps then rescale what they hold in registers
+// and publish the factors with their projected probabilities; warp 17 sees factors other than 1, asks the other
+// service warps in (a sequence number in shared memory that they poll), each multiplies its lane quadrant of the
+// tile's accumulators once the updates issued so far have landed, and only then is the next update issued.
+// Probabilities are at most 2^6 and stay inside fp16; all sums use the same reference maximum, which is what
+// the chunk reports.
 #pragma once
 
-constexpr int W2_T = 896;                 // threads: 8 spectral + 16 score + 4 service warps
-// registers per thread after setmaxnreg: 256 x 88 (spectral) + 512 x 72 (score, as launched) + 128 x 40 (service)
-// = 896 x 72, the registers the CTA holds at launch (the pool setmaxnreg moves them within)
-constexpr int W2_SREG = 88, W2_VREG = 40;
+constexpr int W2_T = 640;                 // threads: 8 spectral + 8 score + 4 service warps
+// registers per thread after setmaxnreg: 256 x 72 (spectral) + 256 x 136 (score) + 128 x 56 (service)
+// <= 640 x 96, the registers the CTA holds at launch (the pool setmaxnreg moves them within)
+constexpr int W2_SREG = 72, W2_QREG = 136, W2_VREG = 56;
 constexpr int W2_MTV = 4;                 // 16-column tiles of verbatim V a score warp owns
 constexpr int W2_KS = 4;                  // 16-column steps of verbatim K a score warp contracts
 constexpr float W2_LAZY = 6.0f;           // log2 headroom before the running maximum moves
-constexpr int W2_TMEM_COLS = 256;         // 4 column tiles x 4 row blocks x 16 columns
+constexpr int W2_TMEM_COLS = 256;         // g: 4 row blocks x 32 columns (4 column tiles x 8 heads); w fragments: 128 columns
+constexpr int W2_TMEM_W = 128;            // first column of the w fragments
+constexpr int W2_IDX = 256;               // verbatim columns per store at most (4 column tiles x 64), KV heads at most 39
 
 struct Ws2Smem {
-  int ec, es, fnt, interp_hi, interp_lo, snode32, snode, pw, ptb, ptp, mx, alpha, lx, bars, slots, total;
+  int ec, es, fnt, interp_hi, interp_lo, snode32, snode, pw, ptb, ptp, mx, alpha, lx, idx, bars, slots, total;
   int fterm, kpad, slot_bytes;
 };
 __host__ __device__ inline Ws2Smem ws2_smem(int N, int Mn_k, int Mn_v) {
@@ -61,13 +67,14 @@ __host__ __device__ inline Ws2Smem ws2_smem(int N, int Mn_k, int Mn_v) {
   s.interp_hi = take(128 * 24 * 2);
   s.interp_lo = take(128 * 24 * 2);
   s.snode32 = take(2 * FD * 32 * 4);          // partial node scores of the two halves of the 2N rows
-  s.snode = take(2 * 2 * 32 * 16 * 2);        // [buffer][hi, lo][head][16 nodes]
-  s.pw = take(16 * 32 * 8 * 2);               // per score warp: probabilities [32 tokens][8 heads]
-  s.ptb = take(4 * 2 * 512);                  // [tile][hi, lo]: B operand [16 rows][16 nodes], rows 8..15 zero
-  s.ptp = take(2 * 4 * 4 * FD * 8 * 4);       // [buffer][tile][quarter][node][head]: projections of the quarters
-  s.mx = take(2 * 4 * 4 * 8 * 4);             // [super-tile parity][tile][quarter][head]
-  s.alpha = take(4 * 8 * 4);
-  s.lx = take(4 * 4 * 8 * 4);
+  s.snode = take(2 * 2 * 32 * 24 * 2);        // [buffer][hi, lo][head][16 nodes, pitch 24]
+  s.pw = take(8 * 64 * 8 * 2);                // per score warp: probabilities [64 tokens][8 heads]
+  s.ptb = take(2 * 1024);                     // [hi, lo]: B operand [32 head columns][16 nodes] as core matrices
+  s.ptp = take(2 * 4 * 2 * FD * 8 * 4);       // [buffer][tile][half][node][head]: projections of the halves
+  s.mx = take(2 * 4 * 2 * 8 * 4);             // [super-tile parity][tile][half][head]
+  s.alpha = take(2 * 4 * 8 * 4);              // [buffer][tile][head]: factor the running maximum's move asks for
+  s.lx = take(4 * 2 * 8 * 4);
+  s.idx = take(2 * (W2_IDX + 40) * 4);         // verbatim column lists of K and V and the KV heads' segment bounds
   s.bars = take(24 * 8);
   const int mnk16 = (Mn_k + 15) / 16 * 16, mnv16 = (Mn_v + 15) / 16 * 16;
   const int w = mnk16 > mnv16 ? mnk16 : mnv16;
@@ -80,7 +87,7 @@ __host__ __device__ inline Ws2Smem ws2_smem(int N, int Mn_k, int Mn_v) {
 }
 
 __device__ __forceinline__ void w2_spec_sync() { asm volatile("bar.sync 1, 256;\n" ::: "memory"); }
-__device__ __forceinline__ void w2_tile_sync(int nt) { asm volatile("bar.sync %0, 128;\n" ::"r"(2 + nt) : "memory"); }
+__device__ __forceinline__ void w2_tile_sync(int nt) { asm volatile("bar.sync %0, 64;\n" ::"r"(2 + nt) : "memory"); }
 
 // shared-memory matrix descriptor of an operand without swizzle: 8 x 8 core matrices of 128 contiguous bytes,
 // K-adjacent ones `lbo` bytes apart, 8-row groups `sbo` bytes apart (descriptor version 1)
@@ -102,6 +109,19 @@ __device__ __forceinline__ void w2_ld8(uint32_t taddr, float (&v)[8]) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+// 16 consecutive columns of this warp's lane quadrant, one lane per thread; completion is awaited separately
+__device__ __forceinline__ void w2_ld16_nowait(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void w2_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void w2_st4(uint32_t taddr, uint4 v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(taddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
 }
 __device__ __forceinline__ void w2_st8(uint32_t taddr, const float (&v)[8]) {
   const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
@@ -128,7 +148,7 @@ __device__ __forceinline__ int w2_foff(int f, int k) { return (f >> 3) * 256 + (
 
 template <typename T>
 __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned char* smem) {
-  constexpr int J = 128, HN = 32, QT = 32;   // tokens per super-tile, head columns per CTA, tokens per quarter
+  constexpr int J = 128, HN = 32;   // tokens per super-tile, head columns per CTA
   constexpr bool kBf16 = !std::is_same<T, __half>::value;
   const fa_decode_args_t& a = p.a;
   const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
@@ -152,15 +172,23 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
   float* mx = reinterpret_cast<float*>(smem + L.mx);
   float* alpha_s = reinterpret_cast<float*>(smem + L.alpha);
   float* lx = reinterpret_cast<float*>(smem + L.lx);
+  int* kn_s = reinterpret_cast<int*>(smem + L.idx);   // copies of kn_list, kn_h, vn_list, vn_h: the score warps index
+  int* knh_s = kn_s + W2_IDX;                          // them at both ends of the chunk, when anything fetched from
+  int* vn_s = knh_s + 40;                              // global memory queues behind the K / V stream
+  int* vnh_s = vn_s + W2_IDX;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars);
   uint64_t* full_slot = bars;         // [3] a K or V half tile has landed
   uint64_t* empty_slot = bars + 3;    // [3] the score warps of its half are done with it
   uint64_t* full_sp = bars + 6;       // [2] node basis + node scores of a super-tile are written
   uint64_t* empty_sp = bars + 8;      // [2] ... and the g update has read the basis
-  uint64_t* pt_full = bars + 10;      // [2] every quarter of every tile has delivered its projected probabilities
+  uint64_t* pt_full = bars + 10;      // [2] both halves of every tile have delivered their projected probabilities
   uint64_t* g_done = bars + 12;       // [1] the g update of a super-tile has completed
+  uint64_t* resc_done = bars + 13;    // [1] the four service warps have rescaled their lane quadrants
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* dead = reinterpret_cast<volatile int*>(bars + 15);
+  volatile int* resc_seq = reinterpret_cast<volatile int*>(bars + 16);   // rescale requests issued so far
+  volatile int* resc_st = reinterpret_cast<volatile int*>(bars + 17);    // super-tile of the latest request
+  volatile int* svc_exit = reinterpret_cast<volatile int*>(bars + 18);   // every g update has been issued
   unsigned char* slots = smem + L.slots;
   const int kpad = L.kpad, ktot = kpad / 16, fterm = L.fterm;
   const int nblk = (kpad + 127) / 128;   // 128-row blocks of g
@@ -168,7 +196,12 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
   const int l0 = chunk * p.mid_chunk;
   const int l1 = min(a.n_mid, l0 + p.mid_chunk);
   const int nst = (l1 - l0 + J - 1) / J;
-  const int n_tiles = 4 * nst;   // per super-tile: K half 0, K half 1, V half 0, V half 1
+  // Half tiles per super-tile, in ring order: K half 0, K half 1, V half 1, V half 0.  A warp reads only the
+  // tiles of its half, i.e. every other phase of a ring slot's barrier, and a parity wait cannot tell "my tile
+  // has landed" from "the tile before the one before mine has not landed yet".  In this order the tile that held
+  // the slot before (three places back) was either read by the same warp or by the warp's tile mate before a
+  // pair barrier the warp has passed since, so it has landed whenever a warp starts to wait.
+  const int n_tiles = 4 * nst;
   const int nbK = (Mn_k + 63) / 64, nbV = (Mn_v + 63) / 64;
   auto slot_of = [&](int bb) { return (int64_t)bb * p.NCH + p.n_il_chunks + chunk; };
 
@@ -176,7 +209,7 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
   auto issue_tile = [&](int i) {
     if (i >= n_tiles) return;
     const int s = i % 3, r = i & 3;
-    const int lf = l0 + (i >> 2) * J + (r & 1) * FH;
+    const int lf = l0 + (i >> 2) * J + ((r == 1 || r == 2) ? FH : 0);
     const bool is_v = r >= 2;
     const int nb = is_v ? nbV : nbK;
     if (lane == 0) mbar_expect_tx(full_slot + s, (uint32_t)(nseq * nb) * 8192u);
@@ -191,15 +224,19 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) {
       mbar_init(full_slot + i, 1);
-      mbar_init(empty_slot + i, 2 * NT);
+      mbar_init(empty_slot + i, NT);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(full_sp + i, 8);
       mbar_init(empty_sp + i, 1);
-      mbar_init(pt_full + i, 4 * NT);
+      mbar_init(pt_full + i, 2 * NT);
     }
     mbar_init(g_done, 1);
+    mbar_init(resc_done, 4);
     *dead = 0;
+    *resc_seq = 0;
+    *resc_st = 0;
+    *svc_exit = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (wp == 0) {
@@ -208,65 +245,64 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   for (int e = tid; e < 2 * FD * 32; e += W2_T) snode32[e] = 0.f;
-  // node basis (rows past 2N of the last 128-row block stay zero) and the B operands (rows 8..15 stay zero)
+  for (int e = tid; e < Mn_k; e += W2_T) kn_s[e] = a.kn_list[e];
+  for (int e = tid; e < Mn_v; e += W2_T) vn_s[e] = a.vn_list[e];
+  for (int e = tid; e <= a.Hkv; e += W2_T) {
+    knh_s[e] = a.kn_h[e];
+    vnh_s[e] = a.vn_h[e];
+  }
+  // node basis (rows past 2N of the last 128-row block stay zero) and the B operand (columns of absent tiles stay zero)
   for (int e = tid; e < (2 * 2 * fterm) / 16; e += W2_T) reinterpret_cast<uint4*>(fnt)[e] = make_uint4(0u, 0u, 0u, 0u);
-  for (int e = tid; e < (4 * 2 * 512) / 16; e += W2_T) reinterpret_cast<uint4*>(ptb)[e] = make_uint4(0u, 0u, 0u, 0u);
+  for (int e = tid; e < (2 * 1024) / 16; e += W2_T) reinterpret_cast<uint4*>(ptb)[e] = make_uint4(0u, 0u, 0u, 0u);
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const uint32_t tmem = *tmem_slot;
-  if (wp == 24) {
+  if (wp == 16) {
     if (lane == 0) {
       if (nbK) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&p.tm_k) : "memory");
       if (nbV) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&p.tm_v) : "memory");
     }
     for (int i = 0; i < 3; ++i) issue_tile(i);
   }
-  for (int e = tid; e < 8 * N; e += W2_T) {
-    const int k = e / N, n = e - k * N;
-    // node 8+k lies (2 x_k - 127) / 2 tokens right of the centre
-    const uint32_t ph = phase_mod((uint64_t)(2 * c_nodes128[8 + k] - (J - 1)), (uint32_t)n, T2);
-    float s, c;
-    sincospif((float)ph * inv_T, &s, &c);
-    ec[e] = c;
-    es[e] = s;
-  }
-  for (int e = tid; e < J * FD; e += W2_T) {
-    const int j = e / FD, k = e - j * FD;
-    __half hi, lo;
-    split_h(g_interp128[e], hi, lo);
-    interp_hi[j * 24 + k] = hi;
-    interp_lo[j * 24 + k] = lo;
+  // node-offset rotation table and interpolation matrix: shared-memory images prepared once per launch
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(p.tab);
+    uint4* dst_e = reinterpret_cast<uint4*>(ec);          // ec and es lie back to back, 8N floats each
+    for (int e = tid; e < 16 * N / 4; e += W2_T) dst_e[e] = __ldg(src + e);
+    uint4* dst_i = reinterpret_cast<uint4*>(interp_hi);   // so do the hi and lo terms, 128 x 24 halves each
+    for (int e = tid; e < 2 * 128 * 24 / 8; e += W2_T) dst_i[e] = __ldg(src + 16 * N / 4 + e);
   }
   __syncthreads();
 
   if (wp < 8) {
     // =========================== spectral warps ================================================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(W2_SREG));
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(W2_SREG));
     const int nt1 = wp & 3, khalf = wp >> 2;
     // this chunk's verbatim-V partial starts from zero (only the verbatim dims are written at the end)
     for (int sq = 0; sq < nseq; ++sq) {
       float* ob = p.o_part + slot_of(b0 + sq) * Hq * D;
       for (int e = tid; e < Hq * D; e += 256) ob[e] = 0.f;
     }
-    // w as persistent B fragments (hi / lo): k = coefficient row, n = head; this warp holds column tile nt1 for part
-    // `khalf` of the 2N rows.  The prepare kernel has written them in fragment order: one 16-byte load per step.
+    // w as B fragments (hi / lo): k = coefficient row, n = head; this warp contracts column tile nt1 over part
+    // `khalf` of the 2N rows.  The prepare kernel has written them in fragment order, 16 bytes per step and lane.
+    // They live in tensor memory (this warp's lane quadrant, 4 columns per step) and are read back for every
+    // super-tile: 64 registers per thread would not survive the basis phase, and anything fetched from L2 while the
+    // K / V stream saturates the memory system takes microseconds.
     constexpr int KH = 16;
     const int kh_steps = (ktot + 1) / 2;
-    uint32_t bhi[KH][2], blo[KH][2];
+    const uint32_t tw = tmem + (uint32_t)(W2_TMEM_W + khalf * 4 * KH) + ((uint32_t)(nt1 * 32) << 16);
     {
-      const int h = 8 * (nt1 % NTs) + gq;
-      const uint4* wf = reinterpret_cast<const uint4*>(p.w) + ((int64_t)(b0 + nt1 / NTs) * Hq + h) * (2 * N / 16) * 4 + tq;
+      const int wh = 8 * (nt1 % NTs) + gq;
+      const uint4* wf = reinterpret_cast<const uint4*>(p.w) + ((int64_t)(b0 + nt1 / NTs) * Hq + wh) * (2 * N / 16) * 4 + tq;
 #pragma unroll
       for (int i = 0; i < KH; ++i) {
         const int ks = khalf * kh_steps + i;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (nt1 < NT && i < kh_steps && h < Hq && ks < ktot) v = __ldg(wf + ks * 4);
-        bhi[i][0] = v.x;
-        bhi[i][1] = v.y;
-        blo[i][0] = v.z;
-        blo[i][1] = v.w;
+        if (nt1 < NT && i < kh_steps && wh < Hq && ks < ktot) v = __ldg(wf + ks * 4);
+        w2_st4(tw + 4 * i, v);
       }
+      asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
     }
     // this thread builds the cosine row n and the sine row N + n of the node basis; phase (modulo 2T) of its
     // frequency at the centre of the first super-tile
@@ -288,75 +324,91 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
         sincospif((float)ph2 * inv_T, &rs, &rc);
         ph2 += d2;
         if (ph2 >= T2) ph2 -= T2;
-        // values of the 16 nodes: node 8 + kp = centre + d_kp, node 7 - kp = centre - d_kp
-        uint32_t ch[8], cl[8], sh[8], sl[8];   // packed pairs of nodes (2i, 2i + 1)
-        float cv[16], sv[16];
-#pragma unroll
-        for (int kp = 0; kp < 8; ++kp) {
-          const float e_c = ec[kp * N + n], e_s = es[kp * N + n];
-          const float t1 = rc * e_c, t2 = rs * e_s, t3 = rs * e_c, t4 = rc * e_s;
-          cv[8 + kp] = t1 - t2;
-          sv[8 + kp] = t3 + t4;
-          cv[7 - kp] = t1 + t2;
-          sv[7 - kp] = t3 - t4;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const __half2 c2 = __floats2half2_rn(cv[2 * i], cv[2 * i + 1]), s2 = __floats2half2_rn(sv[2 * i], sv[2 * i + 1]);
-          const float2 cf = __half22float2(c2), sf = __half22float2(s2);
-          const __half2 c2l = __floats2half2_rn(cv[2 * i] - cf.x, cv[2 * i + 1] - cf.y);
-          const __half2 s2l = __floats2half2_rn(sv[2 * i] - sf.x, sv[2 * i + 1] - sf.y);
-          ch[i] = *reinterpret_cast<const uint32_t*>(&c2);
-          cl[i] = *reinterpret_cast<const uint32_t*>(&c2l);
-          sh[i] = *reinterpret_cast<const uint32_t*>(&s2);
-          sl[i] = *reinterpret_cast<const uint32_t*>(&s2l);
-        }
+        // values of the 16 nodes: node 8 + kp = centre + d_kp, node 7 - kp = centre - d_kp; the lower and the upper
+        // eight in turn (few live registers), each as four packed pairs of neighbouring nodes, hi and lo terms
         const int oc = w2_foff(n, 0), os = w2_foff(N + n, 0);
-        *reinterpret_cast<uint4*>(fh + oc) = make_uint4(ch[0], ch[1], ch[2], ch[3]);
-        *reinterpret_cast<uint4*>(fh + oc + 128) = make_uint4(ch[4], ch[5], ch[6], ch[7]);
-        *reinterpret_cast<uint4*>(fl + oc) = make_uint4(cl[0], cl[1], cl[2], cl[3]);
-        *reinterpret_cast<uint4*>(fl + oc + 128) = make_uint4(cl[4], cl[5], cl[6], cl[7]);
-        *reinterpret_cast<uint4*>(fh + os) = make_uint4(sh[0], sh[1], sh[2], sh[3]);
-        *reinterpret_cast<uint4*>(fh + os + 128) = make_uint4(sh[4], sh[5], sh[6], sh[7]);
-        *reinterpret_cast<uint4*>(fl + os) = make_uint4(sl[0], sl[1], sl[2], sl[3]);
-        *reinterpret_cast<uint4*>(fl + os + 128) = make_uint4(sl[4], sl[5], sl[6], sl[7]);
+#pragma unroll
+        for (int up = 0; up < 2; ++up) {
+          float cv[8], sv[8];
+#pragma unroll
+          for (int kp = 0; kp < 8; ++kp) {
+            const float e_c = ec[kp * N + n], e_s = es[kp * N + n];
+            const float t1 = rc * e_c, t2 = rs * e_s, t3 = rs * e_c, t4 = rc * e_s;
+            if (up) {
+              cv[kp] = t1 - t2;
+              sv[kp] = t3 + t4;
+            } else {
+              cv[7 - kp] = t1 + t2;
+              sv[7 - kp] = t3 - t4;
+            }
+          }
+          uint32_t ch[4], cl[4], sh[4], sl[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const __half2 c2 = __floats2half2_rn(cv[2 * i], cv[2 * i + 1]), s2 = __floats2half2_rn(sv[2 * i], sv[2 * i + 1]);
+            const float2 cf = __half22float2(c2), sf = __half22float2(s2);
+            const __half2 c2l = __floats2half2_rn(cv[2 * i] - cf.x, cv[2 * i + 1] - cf.y);
+            const __half2 s2l = __floats2half2_rn(sv[2 * i] - sf.x, sv[2 * i + 1] - sf.y);
+            ch[i] = *reinterpret_cast<const uint32_t*>(&c2);
+            cl[i] = *reinterpret_cast<const uint32_t*>(&c2l);
+            sh[i] = *reinterpret_cast<const uint32_t*>(&s2);
+            sl[i] = *reinterpret_cast<const uint32_t*>(&s2l);
+          }
+          *reinterpret_cast<uint4*>(fh + oc + 128 * up) = make_uint4(ch[0], ch[1], ch[2], ch[3]);
+          *reinterpret_cast<uint4*>(fl + oc + 128 * up) = make_uint4(cl[0], cl[1], cl[2], cl[3]);
+          *reinterpret_cast<uint4*>(fh + os + 128 * up) = make_uint4(sh[0], sh[1], sh[2], sh[3]);
+          *reinterpret_cast<uint4*>(fl + os + 128 * up) = make_uint4(sl[0], sl[1], sl[2], sl[3]);
+        }
       }
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic writes -> tcgen05.mma reads
       w2_spec_sync();
       // ---- scores at the nodes: s_node[16 x HN] = Fn[16 x 2N] * w[2N x HN] -----------------------
       if (nt1 < NT) {
-        float acc[3][4];
+        // consecutive MMAs never share an accumulator: a dependent MMA would wait out the latency of the one before
+        float acc[6][4];
 #pragma unroll
-        for (int c = 0; c < 3; ++c)
+        for (int c = 0; c < 6; ++c)
 #pragma unroll
           for (int e = 0; e < 4; ++e) acc[c][e] = 0.f;
+        // four steps' fragments per read of tensor memory; the next four are on their way while these are used
+        uint32_t wv[2][16];
+        w2_ld16_nowait(tw, wv[0]);
+        w2_wait_ld();
 #pragma unroll
-        for (int i = 0; i < KH; ++i) {
-          const int ks = khalf * kh_steps + i;
-          if (i < kh_steps && ks < ktot) {
-            uint32_t ah[4], al[4];
-            ldsm_x4_t(ah, fh + ks * 512 + lane * 16);
-            ldsm_x4_t(al, fl + ks * 512 + lane * 16);
-            mma16816<__half>(acc[0], ah, bhi[i]);
-            mma16816<__half>(acc[1], al, bhi[i]);
-            mma16816<__half>(acc[2], ah, blo[i]);
+        for (int c = 0; c < KH / 4; ++c) {
+          if (c + 1 < KH / 4) w2_ld16_nowait(tw + 16 * (c + 1), wv[(c + 1) & 1]);
+#pragma unroll
+          for (int ii = 0; ii < 4; ++ii) {
+            const int i = 4 * c + ii, ks = khalf * kh_steps + i;
+            const uint32_t bhi[2] = {wv[c & 1][4 * ii], wv[c & 1][4 * ii + 1]};
+            const uint32_t blo[2] = {wv[c & 1][4 * ii + 2], wv[c & 1][4 * ii + 3]};
+            if (i < kh_steps && ks < ktot) {
+              uint32_t ah[4], al[4];
+              ldsm_x4_t(ah, fh + ks * 512 + lane * 16);
+              ldsm_x4_t(al, fl + ks * 512 + lane * 16);
+              mma16816<__half>(acc[3 * (i & 1)], ah, bhi);
+              mma16816<__half>(acc[3 * (i & 1) + 1], al, bhi);
+              mma16816<__half>(acc[3 * (i & 1) + 2], ah, blo);
+            }
           }
+          if (c + 1 < KH / 4) w2_wait_ld();
         }
         float* red = snode32 + khalf * (FD * HN);
         const int col = 8 * nt1 + 2 * tq;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) red[(gq + 8 * (e >> 1)) * HN + col + (e & 1)] = (acc[0][e] + acc[1][e]) + acc[2][e];
+        for (int e = 0; e < 4; ++e)
+          red[(gq + 8 * (e >> 1)) * HN + col + (e & 1)] = ((acc[0][e] + acc[3][e]) + (acc[1][e] + acc[4][e])) + (acc[2][e] + acc[5][e]);
       }
       w2_spec_sync();
       {
-        __half* sh_ = snode + (buf * 2 + 0) * 32 * 16;
-        __half* sl_ = snode + (buf * 2 + 1) * 32 * 16;
+        __half* sh_ = snode + (buf * 2 + 0) * 32 * 24;
+        __half* sl_ = snode + (buf * 2 + 1) * 32 * 24;
         for (int e = tid; e < FD * HN; e += 256) {
           const int k = e / HN, h = e - k * HN;
           __half hi, lo;
           split_h(snode32[e] + snode32[FD * HN + e], hi, lo);
-          sh_[h * 16 + k] = hi;
-          sl_[h * 16 + k] = lo;
+          sh_[h * 24 + k] = hi;
+          sl_[h * 24 + k] = lo;
         }
       }
       __syncwarp();
@@ -370,64 +422,91 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
     return;
   }
 
-  if (wp >= 24) {
+  if (wp >= 16) {
     // ============================= service warps ====================================================
-    // Two kinds of events, each polled by its own warp with bounded patience: a ring slot has been released by all
-    // of its readers (warp 24 -> request the half tile three places ahead), and all quarters of all tiles have
-    // delivered the projected probabilities of a super-tile (warp 25 -> add them up, write the B operands, issue
-    // the g update).
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(W2_VREG));
-    if (wp > 25) {
-      __syncthreads();
-      return;
-    }
-    const bool tma_warp = wp == 24;
-    // instruction descriptor of the g update: fp32 accumulator, fp16 A and B, both K-major, N = 16, M = 128
-    const uint32_t idesc = (1u << 4) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-    int t_next = tma_warp ? 3 : n_tiles, m_next = tma_warp ? nst : 0;
-    long long t_last = clock64();
-    while ((t_next < n_tiles || m_next < nst) && !*dead) {
-      bool progress = false;
-      if (t_next < n_tiles) {
-        const int i = t_next - 3;   // the half tile whose slot is reused
-        if (mbar_test(empty_slot + i % 3, (uint32_t)(i / 3) & 1u)) {
-          issue_tile(t_next);
-          ++t_next;
-          progress = true;
+    const int sv = wp - 16;   // role, and (16 being a multiple of 4) the tensor-memory lane quadrant of this warp
+    // Rescale this warp's lane quadrant of every tile whose running maximum moved at super-tile st (st > 0): the
+    // factors lie in alpha_s; the updates issued so far must have landed first.
+    auto rescale_quadrant = [&](int st) {
+      const int buf = st & 1;
+      mbar_wait(g_done, (uint32_t)(st - 1) & 1u, dead, p.err);
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      for (int tile = 0; tile < NT; ++tile) {
+        float av[8];
+        bool any = false;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          av[c] = alpha_s[(buf * 4 + tile) * 8 + c];
+          any = any || av[c] != 1.f;
+        }
+        if (!any) continue;   // (the same for every lane)
+        for (int mb = 0; mb < nblk; ++mb) {
+          float v[8];
+          const uint32_t ta = tmem + (uint32_t)(mb * 32 + tile * 8) + ((uint32_t)(sv * 32) << 16);
+          w2_ld8(ta, v);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) v[c] *= av[c];
+          w2_st8(ta, v);
         }
       }
-      if (m_next < nst && mbar_test(pt_full + (m_next & 1), (uint32_t)(m_next >> 1) & 1u)) {
-        const int st = m_next, buf = st & 1;
-        // the previous update has finished reading the B operands
-        if (st > 0) mbar_wait(g_done, (uint32_t)(st - 1) & 1u, dead, p.err);
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(resc_done);
+    };
+    int resc_seen = 0;
+    if (sv == 1) {
+      // ---- combine + issue: one pass per super-tile ---------------------------------------------------------
+      // instruction descriptor of the g update: fp32 accumulator, fp16 A and B, both K-major, N = 32, M = 128
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(32 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      for (int st = 0; st < nst; ++st) {
+        const int buf = st & 1;
+        mbar_wait(pt_full + buf, (uint32_t)(st >> 1) & 1u, dead, p.err);
+        if (*dead) break;
+        if (st > 0) {
+          const float al = lane < 8 * NT ? alpha_s[buf * 32 + lane] : 1.f;
+          if (__any_sync(0xffffffffu, al != 1.f)) {
+            if (lane == 0) {
+              *resc_st = st;
+              __threadfence_block();
+              *resc_seq = resc_seen + 1;
+            }
+            __syncwarp();
+            rescale_quadrant(st);
+            mbar_wait(resc_done, (uint32_t)resc_seen & 1u, dead, p.err);
+            ++resc_seen;
+          }
+          // the previous update has finished reading the B operands
+          mbar_wait(g_done, (uint32_t)(st - 1) & 1u, dead, p.err);
+        }
         // lane -> (tile, 16 of the tile's 128 (node, head) entries): node = 2 * (lane & 7) + {0, 1}, heads 0..7
         {
           const int tile = lane >> 3, n0 = 2 * (lane & 7);
           if (tile < NT) {
-            const float* src = ptp + ((buf * 4 + tile) * 4) * (FD * 8) + n0 * 8;
-            float v[16];
+            const float* src = ptp + ((buf * 4 + tile) * 2) * (FD * 8) + n0 * 8;
+            unsigned char* bh_ = ptb + tile * 256;   // the tile's 8 head columns: one 8-row group of the operand
+            unsigned char* bl_ = ptb + 1024 + tile * 256;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              float4 acc = *reinterpret_cast<const float4*>(src + 4 * c);
+            for (int c = 0; c < 2; ++c) {
+              // heads 4c .. 4c+3 of the two nodes
+              const float4 a0 = *reinterpret_cast<const float4*>(src + 4 * c);
+              const float4 a1 = *reinterpret_cast<const float4*>(src + FD * 8 + 4 * c);
+              const float4 b0_ = *reinterpret_cast<const float4*>(src + 8 + 4 * c);
+              const float4 b1_ = *reinterpret_cast<const float4*>(src + FD * 8 + 8 + 4 * c);
+              const float va[4] = {a0.x + a1.x, a0.y + a1.y, a0.z + a1.z, a0.w + a1.w};
+              const float vb[4] = {b0_.x + b1_.x, b0_.y + b1_.y, b0_.z + b1_.z, b0_.w + b1_.w};
 #pragma unroll
-              for (int q = 1; q < 4; ++q) {
-                const float4 t = *reinterpret_cast<const float4*>(src + q * (FD * 8) + 4 * c);
-                acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+              for (int i = 0; i < 4; ++i) {
+                // operand element (row h, K index node): core matrix (node >> 3), row h, position node & 7; this
+                // lane's two nodes are neighbours
+                const int h = 4 * c + i;
+                __half h0, l0_, h1, l1_;
+                split_h(va[i], h0, l0_);
+                split_h(vb[i], h1, l1_);
+                const int off = (n0 >> 3) * 128 + h * 16 + (n0 & 7) * 2;
+                *reinterpret_cast<__half2*>(bh_ + off) = __halves2half2(h0, h1);
+                *reinterpret_cast<__half2*>(bl_ + off) = __halves2half2(l0_, l1_);
               }
-              v[4 * c] = acc.x; v[4 * c + 1] = acc.y; v[4 * c + 2] = acc.z; v[4 * c + 3] = acc.w;
-            }
-            unsigned char* bh_ = ptb + (tile * 2 + 0) * 512;
-            unsigned char* bl_ = ptb + (tile * 2 + 1) * 512;
-#pragma unroll
-            for (int h = 0; h < 8; ++h) {
-              // operand element (row h, K index node): core matrix (node >> 3), row h, position node & 7; this
-              // lane's two nodes are neighbours
-              __half h0, l0_, h1, l1_;
-              split_h(v[h], h0, l0_);
-              split_h(v[8 + h], h1, l1_);
-              const int off = (n0 >> 3) * 128 + h * 16 + (n0 & 7) * 2;
-              *reinterpret_cast<__half2*>(bh_ + off) = __halves2half2(h0, h1);
-              *reinterpret_cast<__half2*>(bl_ + off) = __halves2half2(l0_, l1_);
             }
           }
         }
@@ -436,57 +515,120 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
         if (lane == 0) {
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
           const uint32_t fh = smem_u32(fnt + (buf * 2 + 0) * fterm), fl = smem_u32(fnt + (buf * 2 + 1) * fterm);
-          for (int tile = 0; tile < NT; ++tile) {
-            const uint64_t bdh = w2_desc(smem_u32(ptb + (tile * 2 + 0) * 512), 128, 256);
-            const uint64_t bdl = w2_desc(smem_u32(ptb + (tile * 2 + 1) * 512), 128, 256);
-            for (int mb = 0; mb < nblk; ++mb) {
-              const uint64_t adh = w2_desc(fh + mb * 4096, 128, 256), adl = w2_desc(fl + mb * 4096, 128, 256);
-              const uint32_t d = tmem + (uint32_t)(tile * 64 + mb * 16);
-              w2_mma(d, adl, bdh, idesc, st > 0 ? 1u : 0u);
-              w2_mma(d, adh, bdl, idesc, 1u);
-              w2_mma(d, adh, bdh, idesc, 1u);
-            }
+          const uint64_t bdh = w2_desc(smem_u32(ptb), 128, 256), bdl = w2_desc(smem_u32(ptb + 1024), 128, 256);
+          for (int mb = 0; mb < nblk; ++mb) {   // all four column tiles at once: 128 rows x 32 head columns
+            const uint64_t adh = w2_desc(fh + mb * 4096, 128, 256), adl = w2_desc(fl + mb * 4096, 128, 256);
+            const uint32_t d = tmem + (uint32_t)(mb * 32);
+            w2_mma(d, adl, bdh, idesc, st > 0 ? 1u : 0u);
+            w2_mma(d, adh, bdl, idesc, 1u);
+            w2_mma(d, adh, bdh, idesc, 1u);
           }
           w2_commit(empty_sp + buf);   // the basis buffer may be rebuilt once these have been read
           w2_commit(g_done);           // ... and the accumulators are up to date
         }
         __syncwarp();
-        ++m_next;
-        progress = true;
       }
-      if (progress) {
-        t_last = clock64();
-      } else {
-        __nanosleep(60);
-        if (clock64() - t_last > 2000000000LL) {   // about a second without any event: give up
-          *dead = 1;
-          atomicExch(p.err, 1);
+      if (lane == 0) {
+        __threadfence_block();
+        *svc_exit = 1;
+      }
+      __syncwarp();
+    } else {
+      // ---- warp 16 refills the ring; warps 16, 18 and 19 answer rescale requests until warp 17 is through -------
+      int t_next = sv == 0 ? 3 : n_tiles;
+      long long t_last = clock64();
+      while (!*dead) {
+        bool progress = false;
+        if (t_next < n_tiles) {
+          const int i = t_next - 3;   // the half tile whose slot is reused
+          if (mbar_test(empty_slot + i % 3, (uint32_t)(i / 3) & 1u)) {
+            issue_tile(t_next);
+            ++t_next;
+            progress = true;
+          }
+        }
+        int rs = 0, ex = 0;
+        if (lane == 0) {
+          rs = *resc_seq;
+          ex = *svc_exit;
+        }
+        rs = __shfl_sync(0xffffffffu, rs, 0);
+        ex = __shfl_sync(0xffffffffu, ex, 0);
+        if (rs != resc_seen) {
+          __threadfence_block();
+          rescale_quadrant(*resc_st);
+          ++resc_seen;
+          progress = true;
+        } else if (ex && t_next >= n_tiles) {
+          break;   // (warp 17 raises the exit flag only after its last request has been answered)
+        }
+        if (progress) {
+          t_last = clock64();
+        } else {
+          __nanosleep(sv == 0 ? 60 : 400);
+          if (clock64() - t_last > 2000000000LL) {   // about a second without any event: give up
+            *dead = 1;
+            atomicExch(p.err, 1);
+          }
         }
       }
+    }
+    // ---- g of every tile -> g_part[h][row] ----------------------------------------------------------------------
+    // Each service warp moves its lane quadrant of every row block into shared memory (the node-basis buffers: the
+    // last update has read them), head-major like g_part; one bulk copy per tile then takes it to global memory.
+    // (Plain stores from registers, 128 per warp, queue behind the K / V stream of the other CTAs for microseconds.)
+    if (nst > 0) mbar_wait(g_done, (uint32_t)(nst - 1) & 1u, dead, p.err);
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    float* g_s = reinterpret_cast<float*>(fnt);   // [tile][8 heads][2N]
+    for (int tile = 0; tile < NT; ++tile) {
+      for (int mb = 0; mb < nblk; ++mb) {
+        float v[8];
+        w2_ld8(tmem + (uint32_t)(mb * 32 + tile * 8) + ((uint32_t)(sv * 32) << 16), v);
+        const int row = 128 * mb + 32 * sv + lane;
+        if (row < 2 * N) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) g_s[(tile * 8 + c) * 2 * N + row] = nst > 0 ? v[c] : 0.f;
+        }
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic writes -> bulk copy reads
+    asm volatile("bar.sync 6, 128;\n" ::: "memory");
+    if (sv == 0 && lane == 0) {
+      for (int tile = 0; tile < NT; ++tile) {
+        const int sq = tile / NTs, ntl = tile - sq * NTs;
+        const int heads = min(8, Hq - 8 * ntl);
+        float* gb = p.g_part + ((((int64_t)(b0 + sq) * p.n_mid_chunks + chunk) * Hq) + 8 * ntl) * 2 * N;
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(gb), "r"(smem_u32(g_s + tile * 8 * 2 * N)),
+                     "r"((uint32_t)(heads * 2 * N * 4)) : "memory");
+      }
+      asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+      asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");   // shared memory must outlive the reads
     }
     __syncthreads();
     return;
   }
 
   // ============================= score warps ======================================================
-  const int qw = wp - 8, nt = qw >> 2, qt = qw & 3, half = qt >> 1;   // wp % 4 == qt: the tensor-memory lane quadrant
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(W2_QREG));
+  const int qw = wp - 8, nt = qw & 3, half = qw >> 2;
   const bool act = nt < NT;
-  if (!act) {   // no column tile for this warp group
+  if (!act) {   // no column tile for this warp
     __syncthreads();
     return;
   }
   const int sq = nt / NTs, ntl = nt - sq * NTs;   // sequence of this column tile, tile within the sequence
   const int bb = b0 + sq;
-  __half* pw16 = reinterpret_cast<__half*>(smem + L.pw) + qw * QT * 8;   // this warp's probabilities [32 tokens][8 heads]
+  __half* pw16 = reinterpret_cast<__half*>(smem + L.pw) + qw * 64 * 8;   // this warp's probabilities [64 tokens][8 heads]
   T* pwT = reinterpret_cast<T*>(pw16);
   // column ranges of this warp's heads in the verbatim stores
   int kc0, kc1, mtv0, mtvn;
   {
     const int g0 = (8 * ntl) / R, g1 = (min(Hq, 8 * ntl + 8) - 1) / R;
-    kc0 = a.kn_h[g0] & ~15;
-    kc1 = (a.kn_h[g1 + 1] + 15) & ~15;
-    mtv0 = a.vn_h[g0] >> 4;
-    mtvn = ((a.vn_h[g1 + 1] + 15) >> 4) - mtv0;
+    kc0 = knh_s[g0] & ~15;
+    kc1 = (knh_s[g1 + 1] + 15) & ~15;
+    mtv0 = vnh_s[g0] >> 4;
+    mtvn = ((vnh_s[g1 + 1] + 15) >> 4) - mtv0;
   }
   const int nks = (kc1 - kc0) >> 4;   // 16-column steps of the verbatim-K contraction
   // the heads' verbatim-K query entries as MMA B fragments (raw model-dtype values; the softmax scale is
@@ -498,8 +640,8 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
     const int g = h / R;
     int c_lo = 0, c_hi = 0;
     if (h < Hq) {
-      c_lo = a.kn_h[g];
-      c_hi = a.kn_h[g + 1];
+      c_lo = knh_s[g];
+      c_hi = knh_s[g + 1];
     }
 #pragma unroll
     for (int ks = 0; ks < W2_KS; ++ks) {
@@ -507,8 +649,8 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
       for (int r = 0; r < 2; ++r) {
         const int col = kc0 + 16 * ks + 2 * tq + 8 * r;
         T v0 = from_f32<T>(0.f), v1 = from_f32<T>(0.f);
-        if (col >= c_lo && col < c_hi) v0 = q[h * D + a.kn_list[col] - g * D];
-        if (col + 1 >= c_lo && col + 1 < c_hi) v1 = q[h * D + a.kn_list[col + 1] - g * D];
+        if (col >= c_lo && col < c_hi) v0 = q[h * D + kn_s[col] - g * D];
+        if (col + 1 >= c_lo && col + 1 < c_hi) v1 = q[h * D + kn_s[col + 1] - g * D];
         bq[ks][r] = pack_pair<T>(v0, v1);
       }
     }
@@ -517,25 +659,25 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
   const float cst0 = (hl0 < Hq) ? p.cst[(int64_t)bb * Hq + hl0] : 0.f;
   const float cst1 = (hl0 + 1 < Hq) ? p.cst[(int64_t)bb * Hq + hl0 + 1] : 0.f;
   const int cbK = sq * nbK * 64, cbV = sq * nbV * 64;   // first column of this sequence's boxes inside a ring slot
-  const int rq = QT * (qt & 1);                         // first row of this quarter inside its half tile
   float m_run0 = NEG_BIG, m_run1 = NEG_BIG, lsum0 = 0.f, lsum1 = 0.f;
   float Oacc[W2_MTV][4];
 #pragma unroll
   for (int i = 0; i < W2_MTV; ++i)
 #pragma unroll
     for (int e = 0; e < 4; ++e) Oacc[i][e] = 0.f;
-  const uint32_t tm_tile = tmem + (uint32_t)(nt * 64);   // 4 row blocks x 16 columns
 
   for (int st = 0; st < nst; ++st) {
     const int buf = st & 1;
-    const int tok0 = l0 + st * J + QT * qt;   // first token of this warp's quarter
-    float sc[2][4];
+    const int tok0 = l0 + st * J + half * FH;   // first token of this warp's half
+    float sc[4][4];
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) sc[mt][e] = 0.f;
     const int iK = 4 * st + half, sK = iK % 3;
     const uint32_t parK = (uint32_t)(iK / 3) & 1u;
+    // Every run of MMAs below visits four different accumulators in turn: a dependent MMA issued right after
+    // its predecessor would wait out that one's whole latency.
     // ---- verbatim-dim scores from the K rows (needs only the K tile, so it comes first) -----------
     mbar_wait(full_slot + sK, parK, dead, p.err);
     {
@@ -544,16 +686,16 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
       for (int ks = 0; ks < W2_KS; ++ks) {
         if (ks < nks) {
 #pragma unroll
-          for (int mt = 0; mt < 2; ++mt) {
+          for (int mt = 0; mt < 4; ++mt) {
             uint32_t af[4];
-            ldsm_x4(af, ks_ + sw_off(rq + 16 * mt + lds_a_row(lane), (cbK + kc0 + 16 * ks + lds_a_col(lane)) >> 3));
+            ldsm_x4(af, ks_ + sw_off(16 * mt + lds_a_row(lane), (cbK + kc0 + 16 * ks + lds_a_col(lane)) >> 3));
             mma16816<T>(sc[mt], af, bq[ks]);
           }
         }
       }
     }
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
+    for (int mt = 0; mt < 4; ++mt) {
       sc[mt][0] = p.c2 * sc[mt][0] + cst0;
       sc[mt][1] = p.c2 * sc[mt][1] + cst1;
       sc[mt][2] = p.c2 * sc[mt][2] + cst0;
@@ -563,26 +705,31 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
     if (lane == 0) mbar_arrive(empty_slot + sK);
     mbar_wait(full_sp + buf, (st >> 1) & 1, dead, p.err);
     {
-      // ---- add the node scores interpolated to this warp's 32 tokens ---------------------------------
+      // ---- add the node scores interpolated to this warp's 64 tokens ---------------------------------
       uint32_t bh[2], bl[2];
-      const int boff = (8 * nt + lds_b_row(lane)) * 16 + lds_b_col(lane);
-      ldsm_x2(bh, snode + (buf * 2 + 0) * 32 * 16 + boff);
-      ldsm_x2(bl, snode + (buf * 2 + 1) * 32 * 16 + boff);
-      const int ioff = (QT * qt + lds_a_row(lane)) * 24 + lds_a_col(lane);
+      const int boff = (8 * nt + lds_b_row(lane)) * 24 + lds_b_col(lane);
+      ldsm_x2(bh, snode + (buf * 2 + 0) * 32 * 24 + boff);
+      ldsm_x2(bl, snode + (buf * 2 + 1) * 32 * 24 + boff);
+      const int ioff = (half * FH + lds_a_row(lane)) * 24 + lds_a_col(lane);
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
-        uint32_t ah[4], al[4];
+      for (int mt = 0; mt < 4; ++mt) {
+        uint32_t al[4];
         ldsm_x4(al, interp_lo + ioff + 16 * mt * 24);
-        ldsm_x4(ah, interp_hi + ioff + 16 * mt * 24);
         mma16816<__half>(sc[mt], al, bh);
-        mma16816<__half>(sc[mt], ah, bl);
-        mma16816<__half>(sc[mt], ah, bh);
       }
+      uint32_t ah[4][4];
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        ldsm_x4(ah[mt], interp_hi + ioff + 16 * mt * 24);
+        mma16816<__half>(sc[mt], ah[mt], bl);
+      }
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) mma16816<__half>(sc[mt], ah[mt], bh);
     }
-    // ---- softmax over the 128 tokens of the super-tile (the four quarters agree on the maximum) ----------
+    // ---- softmax over the 128 tokens of the super-tile (both halves agree on the maximum) ----------
     float mx0 = NEG_BIG, mx1 = NEG_BIG;
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
+    for (int mt = 0; mt < 4; ++mt) {
       const bool ok0 = (tok0 + 16 * mt + gq) < l1, ok1 = (tok0 + 16 * mt + gq + 8) < l1;
       mx0 = fmaxf(mx0, fmaxf(ok0 ? sc[mt][0] : NEG_BIG, ok1 ? sc[mt][2] : NEG_BIG));
       mx1 = fmaxf(mx1, fmaxf(ok0 ? sc[mt][1] : NEG_BIG, ok1 ? sc[mt][3] : NEG_BIG));
@@ -592,17 +739,14 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
     }
-    // (two copies by super-tile parity: a warp may be a whole super-tile ahead of a tile mate that has not read yet)
+    // (two copies by super-tile parity: a warp may be a whole super-tile ahead of its tile mate, which has not read yet)
     if (gq == 0) {
-      mx[((buf * 4 + nt) * 4 + qt) * 8 + 2 * tq] = mx0;
-      mx[((buf * 4 + nt) * 4 + qt) * 8 + 2 * tq + 1] = mx1;
+      mx[((buf * 4 + nt) * 2 + half) * 8 + 2 * tq] = mx0;
+      mx[((buf * 4 + nt) * 2 + half) * 8 + 2 * tq + 1] = mx1;
     }
     w2_tile_sync(nt);
-    {
-      const float* mr = mx + (buf * 4 + nt) * 32 + 2 * tq;
-      mx0 = fmaxf(fmaxf(mr[0], mr[8]), fmaxf(mr[16], mr[24]));
-      mx1 = fmaxf(fmaxf(mr[1], mr[9]), fmaxf(mr[17], mr[25]));
-    }
+    mx0 = fmaxf(mx0, mx[((buf * 4 + nt) * 2 + (half ^ 1)) * 8 + 2 * tq]);
+    mx1 = fmaxf(mx1, mx[((buf * 4 + nt) * 2 + (half ^ 1)) * 8 + 2 * tq + 1]);
     // lazy running maximum: it moves only when this super-tile exceeds it by more than 2^W2_LAZY
     float al0 = 1.f, al1 = 1.f;
     if (mx0 > m_run0 + W2_LAZY) {
@@ -613,8 +757,12 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
       al1 = exp2f(m_run1 - mx1);
       m_run1 = mx1;
     }
-    const bool moved = __any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f);   // the same in all four warps of the tile
-    if (moved) {
+    // the factors travel with the projected probabilities: the service warps rescale the accumulators in tensor memory
+    if (half == 0 && gq == 0) {
+      alpha_s[(buf * 4 + nt) * 8 + 2 * tq] = al0;
+      alpha_s[(buf * 4 + nt) * 8 + 2 * tq + 1] = al1;
+    }
+    if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
       lsum0 *= al0;
       lsum1 *= al1;
 #pragma unroll
@@ -624,35 +772,12 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
         Oacc[i][2] *= al0;
         Oacc[i][3] *= al1;
       }
-      if (st > 0) {
-        // rescale the tile's accumulators in tensor memory: this warp's lane quadrant of every row block
-        if (qt == 0 && gq == 0) {
-          alpha_s[nt * 8 + 2 * tq] = al0;
-          alpha_s[nt * 8 + 2 * tq + 1] = al1;
-        }
-        mbar_wait(g_done, (uint32_t)(st - 1) & 1u, dead, p.err);   // the updates issued so far have landed
-        w2_tile_sync(nt);
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        float av[8];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) av[c] = alpha_s[nt * 8 + c];
-        for (int mb = 0; mb < nblk; ++mb) {
-          float v[8];
-          const uint32_t ta = tm_tile + (uint32_t)(mb * 16) + ((uint32_t)(qt * 32) << 16);
-          w2_ld8(ta, v);
-#pragma unroll
-          for (int c = 0; c < 8; ++c) v[c] *= av[c];
-          w2_st8(ta, v);
-        }
-        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-        w2_tile_sync(nt);
-      }
     }
-    __half2 ph[2][2];   // probabilities rounded to fp16: (head 2tq, 2tq+1) of token rows gq and gq+8 per 16-token tile
+    __half2 ph[4][2];   // probabilities rounded to fp16: (head 2tq, 2tq+1) of token rows gq and gq+8 per 16-token tile
     {
       float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
+      for (int mt = 0; mt < 4; ++mt) {
         const bool ok0 = (tok0 + 16 * mt + gq) < l1, ok1 = (tok0 + 16 * mt + gq + 8) < l1;
         ph[mt][0] = __floats2half2_rn(ok0 ? exp2f(sc[mt][0] - m_run0) : 0.f, ok0 ? exp2f(sc[mt][1] - m_run1) : 0.f);
         ph[mt][1] = __floats2half2_rn(ok1 ? exp2f(sc[mt][2] - m_run0) : 0.f, ok1 ? exp2f(sc[mt][3] - m_run1) : 0.f);
@@ -665,47 +790,47 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
         s0 += f0.x + f1.x;
         s1 += f0.y + f1.y;
       }
-      lsum0 += s0;   // this thread's rows only; lanes and quarters are added at the end
+      lsum0 += s0;   // this thread's rows only; lanes and halves are added at the end
       lsum1 += s1;
     }
     __syncwarp();
-    // ---- project the probabilities onto the nodes: pt[16 x 8] = Interp^T[16 x 32] * P[32 x 8] ------
-    uint32_t bp[2][2];
+    // ---- project the probabilities onto the nodes: pt[16 x 8] = Interp^T[16 x 64] * P[64 x 8] ------
+    uint32_t bp[4][2];
 #pragma unroll
-    for (int ks = 0; ks < 2; ++ks) ldsm_x2_t(bp[ks], pw16 + (16 * ks + (lane & 15)) * 8);
-    float pt_acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int ks = 0; ks < 4; ++ks) ldsm_x2_t(bp[ks], pw16 + (16 * ks + (lane & 15)) * 8);
     {
-      float pt2[4] = {0.f, 0.f, 0.f, 0.f};
+      float pt4[4][4];
 #pragma unroll
-      for (int ks = 0; ks < 2; ++ks) {
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) pt4[c][e] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
         uint32_t af[4], al_[4];
-        const int ioff = (QT * qt + 16 * ks + lds_at_row(lane)) * 24 + lds_at_col(lane);
+        const int ioff = (half * FH + 16 * ks + lds_at_row(lane)) * 24 + lds_at_col(lane);
         ldsm_x4_t(af, interp_hi + ioff);
         ldsm_x4_t(al_, interp_lo + ioff);
-        mma16816<__half>(pt_acc, af, bp[ks]);
-        mma16816<__half>(pt2, al_, bp[ks]);
+        mma16816<__half>(pt4[2 * (ks & 1)], af, bp[ks]);
+        mma16816<__half>(pt4[2 * (ks & 1) + 1], al_, bp[ks]);
       }
+      // this half's share goes to the service warp, which adds the two up and issues the g update
+      float* dst = ptp + (((buf * 4 + nt) * 2 + half) * FD) * 8;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) pt_acc[e] += pt2[e];
-    }
-    {
-      // this quarter's share goes to the service warp, which adds the four up and issues the g update
-      float* dst = ptp + (((buf * 4 + nt) * 4 + qt) * FD) * 8;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) dst[(gq + 8 * (e >> 1)) * 8 + 2 * tq + (e & 1)] = pt_acc[e];
+      for (int e = 0; e < 4; ++e)
+        dst[(gq + 8 * (e >> 1)) * 8 + 2 * tq + (e & 1)] = (pt4[0][e] + pt4[2][e]) + (pt4[1][e] + pt4[3][e]);
       __syncwarp();
       if (lane == 0) mbar_arrive(pt_full + buf);
     }
     // ---- verbatim-V numerators -------------------------------------------------------------------
-    uint32_t bp_lo[2][2];
+    uint32_t bp_lo[4][2];
     if constexpr (kBf16) {
       // an fp16 value splits exactly into two bf16 values, so the verbatim-V GEMM (model dtype) sees the same
       // probabilities as the spectral side and the denominator
       using T2 = __nv_bfloat162;
-      float2 res[2][2];   // what the bf16 rounding leaves over
+      float2 res[4][2];   // what the bf16 rounding leaves over
       __syncwarp();
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
+      for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
           const float2 f = __half22float2(ph[mt][r]);
@@ -716,29 +841,29 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
         }
       __syncwarp();
 #pragma unroll
-      for (int ks = 0; ks < 2; ++ks) ldsm_x2_t(bp[ks], pwT + (16 * ks + (lane & 15)) * 8);
+      for (int ks = 0; ks < 4; ++ks) ldsm_x2_t(bp[ks], pwT + (16 * ks + (lane & 15)) * 8);
       __syncwarp();
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
+      for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
         for (int r = 0; r < 2; ++r)
           *reinterpret_cast<T2*>(pwT + (16 * mt + gq + 8 * r) * 8 + 2 * tq) = __floats2bfloat162_rn(res[mt][r].x, res[mt][r].y);
       __syncwarp();
 #pragma unroll
-      for (int ks = 0; ks < 2; ++ks) ldsm_x2_t(bp_lo[ks], pwT + (16 * ks + (lane & 15)) * 8);
+      for (int ks = 0; ks < 4; ++ks) ldsm_x2_t(bp_lo[ks], pwT + (16 * ks + (lane & 15)) * 8);
     }
-    const int iV = 4 * st + 2 + half, sV = iV % 3;
+    const int iV = 4 * st + 3 - half, sV = iV % 3;
     const uint32_t parV = (uint32_t)(iV / 3) & 1u;
     mbar_wait(full_slot + sV, parV, dead, p.err);
     {
       const unsigned char* vs_ = slots + sV * L.slot_bytes;
 #pragma unroll
-      for (int ks = 0; ks < 2; ++ks) {
+      for (int ks = 0; ks < 4; ++ks) {
         uint32_t af[W2_MTV][4];
 #pragma unroll
         for (int i = 0; i < W2_MTV; ++i)
           if (i < mtvn)
-            ldsm_x4_t(af[i], vs_ + sw_off(rq + 16 * ks + lds_at_row(lane), (cbV + 16 * (mtv0 + i) + lds_at_col(lane)) >> 3));
+            ldsm_x4_t(af[i], vs_ + sw_off(16 * ks + lds_at_row(lane), (cbV + 16 * (mtv0 + i) + lds_at_col(lane)) >> 3));
 #pragma unroll
         for (int i = 0; i < W2_MTV; ++i)
           if (i < mtvn) mma16816<T>(Oacc[i], af[i], bp[ks]);
@@ -759,53 +884,32 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
     lsum0 += __shfl_xor_sync(0xffffffffu, lsum0, o);
     lsum1 += __shfl_xor_sync(0xffffffffu, lsum1, o);
   }
-  if (gq == 0) {
-    lx[(nt * 4 + qt) * 8 + 2 * tq] = lsum0;
-    lx[(nt * 4 + qt) * 8 + 2 * tq + 1] = lsum1;
+  if (half == 1 && gq == 0) {
+    lx[nt * 8 + 2 * tq] = lsum0;
+    lx[nt * 8 + 2 * tq + 1] = lsum1;
   }
-  // the verbatim-V numerators of the four quarters are added in a fixed order through shared memory (the ring
-  // slots are free: every tile of the chunk has been consumed by this tile's warps only after all loads landed)
-  mbar_wait(g_done, (uint32_t)(nst - 1) & 1u, dead, p.err);
-  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-  // g of this tile: lane quadrant qt of every row block -> g_part[h][row]
-  {
-    float* gb = p.g_part + (((int64_t)bb * p.n_mid_chunks + chunk) * Hq) * 2 * N;
-    for (int mb = 0; mb < nblk; ++mb) {
-      float v[8];
-      w2_ld8(tm_tile + (uint32_t)(mb * 16) + ((uint32_t)(qt * 32) << 16), v);
-      const int row = 128 * mb + 32 * qt + lane;
-      if (row < 2 * N) {
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const int h = 8 * ntl + c;
-          if (h < Hq) gb[(int64_t)h * 2 * N + row] = nst > 0 ? v[c] : 0.f;
-        }
-      }
-    }
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();   // the spectral warps have zeroed this chunk's verbatim-V partial; all ring traffic is over
   {
-    // Oacc of quarters 1..3 -> shared memory (the ring slots), quarter 0 adds them in a fixed order
-    float* red = reinterpret_cast<float*>(slots) + (nt * 3) * (W2_MTV * 4 * 32);
-    if (qt != 0) {
+    // the verbatim-V numerators of the second half -> shared memory (the ring slots are free now), the first half
+    // adds them and writes the chunk's partial
+    float* red = reinterpret_cast<float*>(slots) + nt * (W2_MTV * 4 * 32);
+    if (half == 1) {
 #pragma unroll
       for (int i = 0; i < W2_MTV; ++i)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) red[((qt - 1) * W2_MTV * 4 + i * 4 + e) * 32 + lane] = Oacc[i][e];
+        for (int e = 0; e < 4; ++e) red[(i * 4 + e) * 32 + lane] = Oacc[i][e];
     }
     w2_tile_sync(nt);
-    if (qt == 0) {
+    if (half == 0) {
       const int64_t slot_id = slot_of(bb);
       if (gq == 0) {
-        const float* lr = lx + nt * 32 + 2 * tq;
         if (hl0 < Hq) {
           p.m_part[slot_id * Hq + hl0] = m_run0;
-          p.l_part[slot_id * Hq + hl0] = (lr[0] + lr[8]) + (lr[16] + lr[24]);
+          p.l_part[slot_id * Hq + hl0] = lsum0 + lx[nt * 8 + 2 * tq];
         }
         if (hl0 + 1 < Hq) {
           p.m_part[slot_id * Hq + hl0 + 1] = m_run1;
-          p.l_part[slot_id * Hq + hl0 + 1] = (lr[1] + lr[9]) + (lr[17] + lr[25]);
+          p.l_part[slot_id * Hq + hl0 + 1] = lsum1 + lx[nt * 8 + 2 * tq + 1];
         }
       }
       float* ob = p.o_part + slot_id * Hq * D;
@@ -814,13 +918,12 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
         if (i < mtvn) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int o = (i * 4 + e) * 32 + lane;
-            const float v = Oacc[i][e] + (red[o] + red[W2_MTV * 4 * 32 + o] + red[2 * W2_MTV * 4 * 32 + o]);
+            const float v = Oacc[i][e] + red[(i * 4 + e) * 32 + lane];
             const int c = 16 * (mtv0 + i) + gq + 8 * (e >> 1);
             const int h = hl0 + (e & 1);
             if (c < Mn_v && h < Hq) {
               const int g = h / R;
-              if (c >= a.vn_h[g] && c < a.vn_h[g + 1]) ob[h * D + a.vn_list[c] - g * D] = v;
+              if (c >= vnh_s[g] && c < vnh_s[g + 1]) ob[h * D + vn_s[c] - g * D] = v;
             }
           }
         }

@@ -15,7 +15,7 @@ ANGLE_EXACT, ANGLE_KM57 = _lib.FA_ANGLE_EXACT, _lib.FA_ANGLE_KM57
 
 _scratch = {}
 launch_count = 0          # kernels-launching C-ABI calls made so far (for benchmark accounting)
-last_decode_path = None   # fa_decode_path() of the most recent decode_attn call (0 exact, 1 tensor-core pass, 2 warp-specialised)
+last_decode_path = None   # fa_decode_path() of the most recent decode_attn call (0 exact, 1 tensor-core pass, 2 warp-specialised, 3 warp-specialised with the accumulator in tensor memory)
 
 
 def _dt(t):

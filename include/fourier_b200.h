@@ -184,17 +184,22 @@ typedef struct {
 size_t fa_decode_scratch_bytes(const fa_decode_args_t* args_host);
 /* Which middle-span pass fa_decode_attn will run for these arguments (sizes, strides and pointer
  * alignment are read):
- *   2 = warp-specialised tensor-core pass: the spectral score is evaluated at 16 nodes per 128-token super-tile
- *       and interpolated.  Needs N % 8 == 0, N <= 512, Hq <= 32, head_dim % 16 == 0, 16-byte aligned verbatim rows,
- *       at most 1.5 turns of the highest frequency per super-tile (128 (N - 1) <= 1.5 T), kn_h_host / vn_h_host,
- *       and per 8 query heads at most 64 verbatim-K and 64 verbatim-V columns after rounding to 16.  Above
- *       N = 256 the heads of a sequence are served in groups of 16 by different CTAs.
+ *   3 = warp-specialised tensor-core pass with the spectral accumulator in tensor memory (tcgen05): the spectral
+ *       score is evaluated at 16 nodes per 128-token super-tile and interpolated; the accumulator g and the
+ *       query-side weights w live in tensor memory, g is updated by tcgen05.mma.  Needs what 2 needs and N <= 256,
+ *       8 query heads per column tile (Hq / Hkv one of 1, 2, 4, 8), at most 64 verbatim-K and 64 verbatim-V columns
+ *       per tile after rounding to 16, at most 256 verbatim columns per row, fewer than 40 KV heads.
+ *   2 = the same pass with the accumulator in registers (mma.sync).  Needs N % 8 == 0, N <= 512, Hq <= 32,
+ *       head_dim % 16 == 0, 16-byte aligned verbatim rows, at most 1.5 turns of the highest frequency per super-tile
+ *       (128 (N - 1) <= 1.5 T), kn_h_host / vn_h_host, and per column tile of 8 (or 6) query heads at most 128
+ *       verbatim-K and 128 verbatim-V columns after rounding to 16.  Above N = 256 the heads of a sequence are
+ *       served in groups of 16 by different CTAs.
  *   1 = the same mathematics phase by phase (all warps together): N <= 256, Mn_* <= 256, 64- or 128-token
  *       super-tiles, no host tables needed.
  *   0 = exact CUDA-core pass (any shape).
  *   negative = fa_status_t.
- * Environment: FA_DECODE_EXACT forces 0, FA_DECODE_NO_WS keeps 2 from being chosen, FA_DECODE_WS_TMEM selects
- * the variant of 2 that keeps the spectral accumulator in tensor memory (tcgen05; N <= 256). */
+ * Environment: FA_DECODE_EXACT forces 0, FA_DECODE_NO_WS keeps 2 and 3 from being chosen, FA_DECODE_NO_TMEM
+ * keeps 3 from being chosen. */
 int fa_decode_path(const fa_decode_args_t* args_host);
 int fa_decode_attn(const fa_decode_args_t* args_host, fa_stream_t stream);
 

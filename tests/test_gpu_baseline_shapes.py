@@ -2,7 +2,7 @@
 ``update`` and ``fourier_attention``) and against the CPU oracle -- not against another GPU entry point.
 
 Covered: the Llama-3.1-8B / 32k layer exactly as the benchmark runs it (several sequences per launch, the
-two periods ``T_c = T - 1``, the warp-specialised pass), the single-layer fp16 configuration with its 64
+two periods ``T_c = T - 1``, the warp-specialised pass with the accumulator in tensor memory), the single-layer fp16 configuration with its 64
 decode steps, the Llama-3.2-3B layer (24 query heads, 80 of 128 dims compressed) and one long single
 sequence (131072 tokens, M = 1024).
 
@@ -114,7 +114,7 @@ def test_llama31_8b_32k_layer_as_benchmarked():
     T = 31996 and the projection period is T - 1; four sequences per launch, three decode steps."""
     g = dict(B=4, Hq=32, Hkv=8, D=128, S=4, W=1024, M=512, P=32768, new_tokens=256, mpe=1 << 30, dtype="bf16",
              ncomp=96, seed=4201, T=31996, T_c=31995)
-    _run(g, follow=[0, 3], steps=3, check_steps={0, 1, 2}, faithful_steps={2}, want_path=(2,))
+    _run(g, follow=[0, 3], steps=3, check_steps={0, 1, 2}, faithful_steps={2}, want_path=(3,))
 
 
 def test_single_layer_8k_fp16_64_steps():
@@ -122,7 +122,7 @@ def test_single_layer_8k_fp16_64_steps():
     checked every 8th step and the final state after all 64."""
     g = dict(B=1, Hq=32, Hkv=8, D=128, S=4, W=1024, M=256, P=8192, new_tokens=64, mpe=131072, dtype="fp16",
              ncomp=96, seed=4202, T=7228)
-    _run(g, follow=[0], steps=64, check_steps=set(range(7, 64, 8)) | {0}, faithful_steps={0, 63}, want_path=(1, 2))
+    _run(g, follow=[0], steps=64, check_steps=set(range(7, 64, 8)) | {0}, faithful_steps={0, 63}, want_path=(1, 2, 3))
 
 
 def test_llama32_3b_16k_layer():

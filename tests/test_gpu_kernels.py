@@ -66,6 +66,10 @@ FAST_CASES = {
 WS_CASES = {"fast_gqa4_bf16", "fast_32heads_fp16", "fast_ragged", "fast_one_kv_head", "fast_nothing_verbatim",
             "fast_nothing_compressed", "fast_llama8b_layer", "fast_packed_4seq", "fast_packed_2seq",
             "fast_m1024_head_groups", "fast_m1024_three_tiles", "fast_gqa3_six_head_tiles", "fast_gqa3_ragged"}
+# of those, the shapes that keep the spectral accumulator in tensor memory (at most 512 coefficient rows,
+# column tiles of 8 query heads with at most 64 verbatim K and V columns each)
+TMEM_CASES = WS_CASES - {"fast_m1024_head_groups", "fast_m1024_three_tiles", "fast_gqa3_six_head_tiles", "fast_gqa3_ragged",
+                         "fast_ragged"}
 # of those, the shapes only the warp-specialised form takes (more than 512 coefficient rows)
 WS_ONLY_CASES = {"fast_m1024_head_groups", "fast_m1024_three_tiles", "fast_gqa3_six_head_tiles"}
 
@@ -88,8 +92,14 @@ def test_decode_attn_tensor_core_pass(name, monkeypatch):
         assert attn_err_excess(host(out), ref, g["dtype"]) <= 0
 
     out = ops.decode_attn(qd, num_head_q=g["Hq"], num_head_kv=g["Hkv"], T=oc.T, **inp)
-    assert ops.last_decode_path == (2 if name in WS_CASES else 1), ops.last_decode_path
+    want = (3 if name in TMEM_CASES else 2) if name in WS_CASES else 1
+    assert ops.last_decode_path == want, ops.last_decode_path
     check_tensor_core_result(out)
+    if ops.last_decode_path == 3:   # the same shape with the accumulator in registers
+        monkeypatch.setenv("FA_DECODE_NO_TMEM", "1")
+        out = ops.decode_attn(qd, num_head_q=g["Hq"], num_head_kv=g["Hkv"], T=oc.T, **inp)
+        assert ops.last_decode_path == 2, ops.last_decode_path
+        check_tensor_core_result(out)
     if ops.last_decode_path == 2:
         monkeypatch.setenv("FA_DECODE_NO_WS", "1")
         out = ops.decode_attn(qd, num_head_q=g["Hq"], num_head_kv=g["Hkv"], T=oc.T, **inp)
@@ -101,12 +111,14 @@ def test_decode_attn_tensor_core_pass(name, monkeypatch):
     assert np.abs(host(exact) - ideal).max() <= 3e-5 * max(1.0, np.abs(ideal).max())
 
 
-def _state_ramp(g):
+def _state_ramp(g, steep=False):
     """Like _state, but the keys grow along the sequence, so the running maxima of the softmax keep
-    rising from tile to tile and every accumulator is rescaled again and again."""
+    rising from tile to tile and every accumulator is rescaled again and again (steep: by more than 2^6 from
+    one 128-token tile to the next here and there, which is what makes the accumulators kept in tensor memory
+    move)."""
     tables, k, v, qs = case_inputs(g)
     P = g["P"]
-    ramp = (0.2 + 2.8 * np.arange(k.shape[2]) / P).astype(np.float32)
+    ramp = ((0.02 + 12.0 * (np.arange(k.shape[2]) / P) ** 2) if steep else (0.2 + 2.8 * np.arange(k.shape[2]) / P)).astype(np.float32)
     k = fo.rnd(k.astype(np.float32) * ramp[None, None, :, None], g["dtype"])
     oc = oracle_cache(g, tables)
     oc.update(k[:, :, :P], v[:, :, :P], 0)
@@ -114,21 +126,25 @@ def _state_ramp(g):
     return oc, qs[0]
 
 
-@pytest.mark.parametrize("name", ["fast_32heads_fp16", "fast_gqa4_bf16", "fast_gqa3_half_tiles"])
-def test_decode_attn_rising_scores(name, monkeypatch):
+@pytest.mark.parametrize("steep", [False, True])
+@pytest.mark.parametrize("name", ["fast_32heads_fp16", "fast_gqa4_bf16", "fast_gqa3_half_tiles", "fast_llama8b_layer"])
+def test_decode_attn_rising_scores(name, steep, monkeypatch):
     import fourierattention_b200.ops as ops
     g = FAST_CASES[name]
-    oc, q = _state_ramp(g)
+    oc, q = _state_ramp(g, steep)
     inp = decode_inputs_from_oracle(oc, g["dtype"])
     qd = dev(q, g["dtype"])
     ideal = oc.attend(q, 0, g["Hq"], g["Hkv"], faithful=False)[:, :, 0]
-    for env in (None, "FA_DECODE_NO_WS"):
+    seen = []
+    for env in (None, "FA_DECODE_NO_TMEM", "FA_DECODE_NO_WS"):
         if env:
             monkeypatch.setenv(env, "1")
         out = ops.decode_attn(qd, num_head_q=g["Hq"], num_head_kv=g["Hkv"], T=oc.T, **inp)
-        assert ops.last_decode_path in (1, 2)
+        assert ops.last_decode_path in (1, 2, 3)
+        seen.append(ops.last_decode_path)
         err = np.abs(host(out) - ideal).max()
         assert err <= 1.5e-4 * max(1.0, np.abs(ideal).max()), (env, err)
+    assert seen == ([3, 2, 1] if name in TMEM_CASES else [1, 1, 1]), seen
 
 
 def _state(g):

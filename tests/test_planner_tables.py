@@ -47,17 +47,20 @@ def test_shipped_tables_reach_the_tensor_core_passes(L):
     for name, layers in tables.items():
         Hq = 32 if "8b" in name else 24
         p512 = _paths(L, layers, Hq, 512, 32768)
-        assert all(p in (0, 1, 2) for p in p512)
-        fast_layers += sum(p in (1, 2) for p in p512)
+        assert all(p in (0, 1, 2, 3) for p in p512)
+        fast_layers += sum(p in (1, 2, 3) for p in p512)
         total += len(p512)
         # M = 1024 needs a context long enough that the top frequency turns at most 1.5 times per 128-token
         # super-tile (T >= 43605); at 64k most layers the M = 512 plan takes are taken again (the single, larger
         # node-basis buffer leaves less shared memory for wide verbatim rows)
         p1024 = _paths(L, layers, Hq, 1024, 65536)
-        assert all(a == 2 for a, b in zip(p512, p1024) if b == 2), name
+        assert all(a in (2, 3) for a, b in zip(p512, p1024) if b == 2), name
         wide_layers += sum(p == 2 for p in p1024)
     # 22 of 32 layers of the Llama-3.1-8B table and 15 to 20 of 28 of each Llama-3.2-3B table take the
     # warp-specialised pass, a few more the phase-by-phase pass
     assert fast_layers >= 170 and total == 228 and wide_layers >= 100, (fast_layers, total, wide_layers)
     p8b = _paths(L, tables["llama3.1-8b-fourier/compressed_dims_32k_1024states_splithead.json"], 32, 512, 32768)
-    assert sum(p == 2 for p in p8b) >= 22
+    assert sum(p in (2, 3) for p in p8b) >= 22
+    # ... those whose column tiles of 8 heads find at most 64 verbatim K and V columns with the spectral accumulator
+    # in tensor memory (4 layers of this table; a uniform 96-of-128 split, as the benchmark uses, always does)
+    assert sum(p == 3 for p in p8b) >= 4, p8b

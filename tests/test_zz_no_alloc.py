@@ -47,18 +47,19 @@ def test_static_scratch_matches_on_two_calls_in_a_row():
 
 def test_static_scratch_on_the_tensor_core_passes_with_changing_plans():
     """The shared buffer keeps whatever the previous call left in it, and consecutive calls here have
-    different chunk counts, batch sizes and sequences per CTA (a warp-specialised plan, an exact-kernel
-    plan, a warp-specialised plan that packs four sequences per CTA with a batch of five, a 64-token
-    super-tile plan): every word a call reads must have been written by that same call."""
+    different chunk counts, batch sizes and sequences per CTA (a warp-specialised plan with the accumulator in
+    tensor memory, an exact-kernel plan, such a plan that packs four sequences per CTA with a batch of five, a
+    64-token super-tile plan, a warp-specialised plan with six-head column tiles and the accumulator in
+    registers): every word a call reads must have been written by that same call."""
     seen = set()
     for name in ("fast_32heads_fp16", "wide", "fast_packed_4seq", "fast_gqa3_half_tiles", "fast_packed_2seq",
-                 "gqa3_bf16", "fast_llama8b_layer", "fast_packed_4seq"):
+                 "gqa3_bf16", "fast_llama8b_layer", "fast_gqa3_six_head_tiles", "fast_packed_4seq"):
         want, got, path, ideal = _both(name)
         seen.add(path)
         for w, g_ in zip(want, got):
             assert np.abs(host(w) - host(g_)).max() <= 2e-6, name
         assert np.abs(host(got[0]) - ideal).max() <= 1.5e-4 * max(1.0, np.abs(ideal).max()), name
-    assert seen == {0, 1, 2}, seen
+    assert seen == {0, 1, 2, 3}, seen
 
 
 def test_static_scratch_allocates_nothing_and_rejects_oversize():
