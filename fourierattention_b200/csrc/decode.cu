@@ -1238,8 +1238,12 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
       // grows with rows x KV heads (7.2 K ticks for 16 rows x 8 heads)
       // (the warp-specialised kernels run 16-row tiles through a pass unrolled for exactly one 16-row block: 5.6 K
       // ticks per tile at 8 KV heads)
-      const double cost_il_tile = (p.fast == 2 && p.TRm == 16) ? 2000.0 + 28.0 * p.TRm * a.Hkv : 2500.0 + 37.0 * p.TRm * a.Hkv;
-      const double cost_mid_tok = p.fast == 2 ? (p.wsGN == 2 ? 130.0 : 100.0) : 142.0;
+      // (next to middle-span CTAs of the tensor-memory form, which leave it less of the memory system, the same pass
+      // was measured at 6.4 K ticks per tile; those CTAs take 7.5 K ticks per 128-token super-tile and 40 K of set-up)
+      const bool tm = p.fast == 2 && p.ws2;
+      const double cost_il_tile = (p.fast == 2 && p.TRm == 16) ? 2000.0 + (tm ? 34.0 : 28.0) * p.TRm * a.Hkv : 2500.0 + 37.0 * p.TRm * a.Hkv;
+      const double cost_mid_tok = p.fast == 2 ? (tm ? 60.0 : p.wsGN == 2 ? 130.0 : 100.0) : 142.0;
+      const double cost_mid_fix = tm ? 40000.0 : 24000.0;
       const int n_tiles = ceil_div(a.n_sink, p.TRm) + ceil_div(a.n_win, p.TRm);
       double best = 1e30;
       int best_il = 1;
@@ -1250,7 +1254,7 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
         if (n_mid < 1) break;
         if (n_mid > max_chunks) n_mid = max_chunks;
         const int mid_tok = rup(ceil_div(n_mid_r, n_mid), J);
-        const double t_il = 8000.0 + cost_il_tile * tpc, t_mid = 24000.0 + cost_mid_tok * mid_tok;
+        const double t_il = 8000.0 + cost_il_tile * tpc, t_mid = cost_mid_fix + cost_mid_tok * mid_tok;
         const double t = t_il > t_mid ? t_il : t_mid;
         if (t < best) {
           best = t;

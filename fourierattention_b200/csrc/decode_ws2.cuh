@@ -189,6 +189,7 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
   volatile int* resc_seq = reinterpret_cast<volatile int*>(bars + 16);   // rescale requests issued so far
   volatile int* resc_st = reinterpret_cast<volatile int*>(bars + 17);    // super-tile of the latest request
   volatile int* svc_exit = reinterpret_cast<volatile int*>(bars + 18);   // every g update has been issued
+  uint64_t* tab_bar = bars + 19;      // [1] the tables have landed
   unsigned char* slots = smem + L.slots;
   const int kpad = L.kpad, ktot = kpad / 16, fterm = L.fterm;
   const int nblk = (kpad + 127) / 128;   // 128-row blocks of g
@@ -221,6 +222,9 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
   };
 
   // ---- set-up (all warps) ---------------------------------------------------------------------
+  // the index lists first: their latency (global memory) passes while the rest of the set-up runs
+  const int kn_v = tid < Mn_k ? a.kn_list[tid] : 0, vn_v = tid < Mn_v ? a.vn_list[tid] : 0;
+  const int knh_v = tid <= a.Hkv ? a.kn_h[tid] : 0, vnh_v = tid <= a.Hkv ? a.vn_h[tid] : 0;
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) {
       mbar_init(full_slot + i, 1);
@@ -233,11 +237,21 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
     }
     mbar_init(g_done, 1);
     mbar_init(resc_done, 4);
+    mbar_init(tab_bar, 1);
     *dead = 0;
     *resc_seq = 0;
     *resc_st = 0;
     *svc_exit = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    // node-offset rotation table (ec and es lie back to back, 8N floats each) and interpolation matrix (hi and lo
+    // terms back to back, 128 x 24 halves each): shared-memory images prepared once per launch, fetched by two
+    // bulk copies while the set-up goes on
+    const uint32_t b_e = 64u * (uint32_t)N, b_i = 2u * 128u * 24u * 2u;
+    mbar_expect_tx(tab_bar, b_e + b_i);
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(smem_u32(ec)),
+                 "l"(p.tab), "r"(b_e), "r"(smem_u32(tab_bar)) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                     smem_u32(interp_hi)), "l"(p.tab + 16 * N), "r"(b_i), "r"(smem_u32(tab_bar)) : "memory");
   }
   if (wp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)),
@@ -245,15 +259,16 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   for (int e = tid; e < 2 * FD * 32; e += W2_T) snode32[e] = 0.f;
-  for (int e = tid; e < Mn_k; e += W2_T) kn_s[e] = a.kn_list[e];
-  for (int e = tid; e < Mn_v; e += W2_T) vn_s[e] = a.vn_list[e];
-  for (int e = tid; e <= a.Hkv; e += W2_T) {
-    knh_s[e] = a.kn_h[e];
-    vnh_s[e] = a.vn_h[e];
-  }
-  // node basis (rows past 2N of the last 128-row block stay zero) and the B operand (columns of absent tiles stay zero)
-  for (int e = tid; e < (2 * 2 * fterm) / 16; e += W2_T) reinterpret_cast<uint4*>(fnt)[e] = make_uint4(0u, 0u, 0u, 0u);
+  // rows past 2N of the node basis' last 128-row block stay zero, and so do the B operand's columns of absent tiles
+  for (int t = 0; t < 4; ++t)
+    for (int e = 2 * N * 32 / 16 + tid; e < fterm / 16; e += W2_T) reinterpret_cast<uint4*>(fnt + t * fterm)[e] = make_uint4(0u, 0u, 0u, 0u);
   for (int e = tid; e < (2 * 1024) / 16; e += W2_T) reinterpret_cast<uint4*>(ptb)[e] = make_uint4(0u, 0u, 0u, 0u);
+  if (tid < Mn_k) kn_s[tid] = kn_v;
+  if (tid < Mn_v) vn_s[tid] = vn_v;
+  if (tid <= a.Hkv) {
+    knh_s[tid] = knh_v;
+    vnh_s[tid] = vnh_v;
+  }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -265,25 +280,11 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
     }
     for (int i = 0; i < 3; ++i) issue_tile(i);
   }
-  // node-offset rotation table and interpolation matrix: shared-memory images prepared once per launch
-  {
-    const uint4* src = reinterpret_cast<const uint4*>(p.tab);
-    uint4* dst_e = reinterpret_cast<uint4*>(ec);          // ec and es lie back to back, 8N floats each
-    for (int e = tid; e < 16 * N / 4; e += W2_T) dst_e[e] = __ldg(src + e);
-    uint4* dst_i = reinterpret_cast<uint4*>(interp_hi);   // so do the hi and lo terms, 128 x 24 halves each
-    for (int e = tid; e < 2 * 128 * 24 / 8; e += W2_T) dst_i[e] = __ldg(src + 16 * N / 4 + e);
-  }
-  __syncthreads();
 
   if (wp < 8) {
     // =========================== spectral warps ================================================
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(W2_SREG));
     const int nt1 = wp & 3, khalf = wp >> 2;
-    // this chunk's verbatim-V partial starts from zero (only the verbatim dims are written at the end)
-    for (int sq = 0; sq < nseq; ++sq) {
-      float* ob = p.o_part + slot_of(b0 + sq) * Hq * D;
-      for (int e = tid; e < Hq * D; e += 256) ob[e] = 0.f;
-    }
     // w as B fragments (hi / lo): k = coefficient row, n = head; this warp contracts column tile nt1 over part
     // `khalf` of the 2N rows.  The prepare kernel has written them in fragment order, 16 bytes per step and lane.
     // They live in tensor memory (this warp's lane quadrant, 4 columns per step) and are read back for every
@@ -313,6 +314,12 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
       ph2 = phase_mod(centre2 % (uint64_t)T2, (uint32_t)n, T2);
       d2 = phase_mod((uint64_t)(2 * J), (uint32_t)n, T2);
     }
+    // this chunk's verbatim-V partial starts from zero (only the verbatim dims are written at the end)
+    for (int sq = 0; sq < nseq; ++sq) {
+      float* ob = p.o_part + slot_of(b0 + sq) * Hq * D;
+      for (int e = tid; e < Hq * D; e += 256) ob[e] = 0.f;
+    }
+    mbar_wait(tab_bar, 0, dead, p.err);
     for (int j = 0; j < nst; ++j) {
       const int buf = j & 1;
       unsigned char* fh = fnt + (buf * 2 + 0) * fterm;
@@ -666,6 +673,7 @@ __device__ void mid_chunk_ws2(const DecodeParams& p, int b0, int chunk, unsigned
 #pragma unroll
     for (int e = 0; e < 4; ++e) Oacc[i][e] = 0.f;
 
+  mbar_wait(tab_bar, 0, dead, p.err);
   for (int st = 0; st < nst; ++st) {
     const int buf = st & 1;
     const int tok0 = l0 + st * J + half * FH;   // first token of this warp's half
