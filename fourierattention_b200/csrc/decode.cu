@@ -817,8 +817,14 @@ __global__ void __launch_bounds__(W2_T, 1) decode_main_ws2_kernel(const __grid_c
     asm volatile("setmaxnreg.inc.sync.aligned.u32 112;\n");
     const int seq = blockIdx.x / p.n_il_chunks, chunk = blockIdx.x - seq * p.n_il_chunks;
     if (b * p.wsSEQ + seq >= p.a.B) return;
-    if (p.TRm == 16)   // wide rows (Hkv*D = 1024): 16-row tiles, the common case, unrolled for exactly one
+    // unrolled for exactly the 16-row blocks a tile of rows has (16 rows at Hkv*D = 1024, 32 at 512, 64 at 256): the
+    // pass has 112 registers here, and what it spills is reloaded from L2 behind the K / V stream of the other CTAs
+    if (p.TRm == 16)
       il_chunk_mma<T, 1>(p, b * p.wsSEQ + seq, chunk, smem_raw);
+    else if (p.TRm == 32)
+      il_chunk_mma<T, 2>(p, b * p.wsSEQ + seq, chunk, smem_raw);
+    else if (p.TRm == 64)
+      il_chunk_mma<T, 4>(p, b * p.wsSEQ + seq, chunk, smem_raw);
     else
       il_chunk_mma<T>(p, b * p.wsSEQ + seq, chunk, smem_raw);
   } else {
