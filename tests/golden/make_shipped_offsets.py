@@ -1,9 +1,9 @@
 """Writes ``shipped_table_offsets.json``: the cumulative per-head counts (``kc_h_list``, ``kn_h_list``,
 ``vc_h_list``, ``vn_h_list``) of every ``_splithead`` dim table the reference ships under
 ``compressed_dims_file/`` -- the only part of those tables the decode planner looks at.  Needs a checkout of
-the reference (first argument, default /root/reference); the fixture it writes is what the tests read.
+the reference (first argument); the fixture it writes is what the tests read.
 
-    python tests/golden/make_shipped_offsets.py [reference_dir]
+    python tests/golden/make_shipped_offsets.py <reference_dir>
 """
 import glob
 import json
@@ -12,7 +12,9 @@ import sys
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit(__doc__)
+    ref = sys.argv[1]
     base = os.path.join(ref, "compressed_dims_file")
     out = {}
     for f in sorted(glob.glob(os.path.join(base, "*", "*_splithead.json"))):
