@@ -823,10 +823,8 @@ __global__ void __launch_bounds__(W2_T, 1) decode_main_ws2_kernel(const __grid_c
       il_chunk_mma<T, 1>(p, b * p.wsSEQ + seq, chunk, smem_raw);
     else if (p.TRm == 32)
       il_chunk_mma<T, 2>(p, b * p.wsSEQ + seq, chunk, smem_raw);
-    else if (p.TRm == 64)
+    else   // (the planner keeps tiles of rows at 64 rows or fewer for this kernel)
       il_chunk_mma<T, 4>(p, b * p.wsSEQ + seq, chunk, smem_raw);
-    else
-      il_chunk_mma<T>(p, b * p.wsSEQ + seq, chunk, smem_raw);
   } else {
     mid_chunk_ws2<T>(p, b * p.wsSEQ, blockIdx.x - n_il_ctas, smem_raw);
   }
@@ -1209,6 +1207,17 @@ static int make_plan(const fa_decode_args_t& a, DecodeParams& p, const PlanFlags
         if (ok && need <= 227 * 1024 && (nbK > nbV ? nbK : nbV) <= 32) {
           p.fast = 2;
           p.w_frag = 1;
+          if (p.ws2) {
+            // The sinks+window pass has 112 registers inside the tensor-memory kernel, and what it spills is reloaded
+            // from L2 behind the K / V stream: tiles of at most 32 rows (two 16-row blocks, no spills), 64 rows with a
+            // single KV head (measured: 2 KV heads 3.45 -> 3.02 ms per step with 32-row tiles, 1 KV head 3.07 ->
+            // 2.95 ms with 64-row tiles at the Llama-3.1-8B shard shapes)
+            const int cap = a.Hkv == 1 ? 64 : 32;
+            if (p.TRm > cap) {
+              p.TRm = cap;
+              il_smem_fast = il_mma_smem(cap, p.F, a.Hkv, a.D, a.dtype == FA_DTYPE_BF16).total;
+            }
+          }
           p.wsSEQ = seq;
           p.wsNTs = NT;
           p.wsGN = GN;
