@@ -139,3 +139,42 @@ def test_long_single_sequence_131k():
     # |C| reaches ~1e3 at this span, so the absolute 2e-3 contract sits at the float32 rounding floor of the
     # coefficients themselves; the allowance grows with their size here (4e-6 relative to the largest one)
     _run(g, follow=[0], steps=2, check_steps={0, 1}, faithful_steps=set(), want_path=(2,), coef_rel=4e-6)
+
+
+def test_llama31_8b_32k_kv_head_shards_as_benchmarked():
+    """The shards the 4- and 8-GPU benchmark lines run: 2 of 8 and 1 of 8 KV heads of the Llama-3.1-8B / 32k layer
+    (``kv_head_range``), eight sequences, so that four sequences share a CTA of the warp-specialised pass and the
+    sinks+window rows go through tiles of 32 and 64 rows.  Each shard is compared with the same heads of the
+    unsharded cache, which the test above holds to the oracle; the chunk plans differ, so the results agree to
+    rounding."""
+    from fourierattention_b200 import DynamicCache, ops
+    g = dict(B=8, Hq=32, Hkv=8, D=128, S=4, W=1024, M=512, P=32768, new_tokens=256, mpe=1 << 30, dtype="bf16",
+             ncomp=96, seed=4205)
+    dt, P, D, R, steps = g["dtype"], g["P"], g["D"], g["Hq"] // g["Hkv"], 2
+    tables = fo.make_splithead_tables(1, g["Hkv"], D, g["ncomp"], g["seed"])
+    k, v = fo.synth_kv(g["seed"], g["B"], g["Hkv"], P + steps, D, dt)
+    rng = np.random.default_rng(g["seed"] + 1000)
+    qs = fo.rnd(rng.standard_normal((steps, g["B"], g["Hq"] * D)).astype(np.float32), dt)
+    ranges = ((2, 4), (7, 8))
+    path = write_tables(tables)
+    try:
+        full = DynamicCache(_config(g, path))
+        shards = [DynamicCache(_config(g, path), kv_head_range=r) for r in ranges]
+    finally:
+        os.unlink(path)
+    full.update(update_arg(k[:, :, :P], dt), update_arg(v[:, :, :P], dt), 0)
+    for c, (h0, h1) in zip(shards, ranges):
+        c.update(update_arg(k[:, h0:h1, :P], dt), update_arg(v[:, h0:h1, :P], dt), 0)
+    for s in range(steps):
+        sl = slice(P + s, P + s + 1)
+        full.update(update_arg(k[:, :, sl], dt), update_arg(v[:, :, sl], dt), 0)
+        want = host(full.fourier_attention(dev(qs[s], dt), 0, g["Hq"]))
+        assert ops.last_decode_path == 3
+        for c, (h0, h1) in zip(shards, ranges):
+            c.update(update_arg(k[:, h0:h1, sl], dt), update_arg(v[:, h0:h1, sl], dt), 0)
+            ql = qs[s].reshape(g["B"], g["Hq"], D)[:, h0 * R:h1 * R].reshape(g["B"], -1)
+            got = host(c.fourier_attention(dev(ql, dt), 0, (h1 - h0) * R))
+            assert ops.last_decode_path == 3, ops.last_decode_path
+            ref = want[:, h0 * R:h1 * R]
+            assert np.isfinite(got).all()
+            assert np.abs(got - ref).max() <= 1e-4 * max(1.0, np.abs(ref).max()), (s, (h0, h1), np.abs(got - ref).max())
