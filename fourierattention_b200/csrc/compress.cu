@@ -221,6 +221,43 @@ __global__ void evict_update_kernel(float* __restrict__ k_coef, const T* __restr
     }
   }
   float* cb = coef + (int64_t)b * 2 * N * Mc;
+  if ((Mc & 3) == 0 && (reinterpret_cast<uintptr_t>(cb) & 15) == 0) {
+    // four columns per thread: every load of the update is requested before the first value is used, so a CTA
+    // pays one trip to memory instead of one per row (same arithmetic per element)
+    for (int m = 4 * threadIdx.x; m < Mc; m += 4 * blockDim.x) {
+      float xv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) xv[j] = to_f32(row[idx ? idx[m + j] : m + j]);
+      float4 vc[EV_ROWS], vs[EV_ROWS];
+#pragma unroll
+      for (int r = 0; r < EV_ROWS; ++r) {
+        const int n = n0 + r;
+        if (n < N) {
+          vc[r] = *reinterpret_cast<const float4*>(cb + (int64_t)n * Mc + m);
+          vs[r] = *reinterpret_cast<const float4*>(cb + (int64_t)(N + n) * Mc + m);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < EV_ROWS; ++r) {
+        const int n = n0 + r;
+        if (n < N) {
+          // one rounding per term, as `base + increment` of the reference (KM:856)
+          float4 oc, os;
+          oc.x = __fadd_rn(vc[r].x, __fmul_rn(c[r], xv[0]));
+          oc.y = __fadd_rn(vc[r].y, __fmul_rn(c[r], xv[1]));
+          oc.z = __fadd_rn(vc[r].z, __fmul_rn(c[r], xv[2]));
+          oc.w = __fadd_rn(vc[r].w, __fmul_rn(c[r], xv[3]));
+          os.x = __fadd_rn(vs[r].x, __fmul_rn(s[r], xv[0]));
+          os.y = __fadd_rn(vs[r].y, __fmul_rn(s[r], xv[1]));
+          os.z = __fadd_rn(vs[r].z, __fmul_rn(s[r], xv[2]));
+          os.w = __fadd_rn(vs[r].w, __fmul_rn(s[r], xv[3]));
+          *reinterpret_cast<float4*>(cb + (int64_t)n * Mc + m) = oc;
+          *reinterpret_cast<float4*>(cb + (int64_t)(N + n) * Mc + m) = os;
+        }
+      }
+    }
+    return;
+  }
   for (int m = threadIdx.x; m < Mc; m += blockDim.x) {
     const float xv = to_f32(row[idx ? idx[m] : m]);
 #pragma unroll
