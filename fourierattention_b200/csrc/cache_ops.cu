@@ -51,9 +51,10 @@ template <typename T>
 __global__ void colstats_kernel(const T* __restrict__ x, int K, int64_t x_sb, int64_t x_sk,
                                 const int32_t* __restrict__ idx, int Mc, float* __restrict__ avg,
                                 float* __restrict__ dev) {
-  __shared__ double s_sum[8][32];
-  __shared__ float s_max[8][32];
-  __shared__ float s_min[8][32];
+  constexpr int NW = 32;   // warps per CTA: the walk down the rows is bound by the loads in flight, so as many as fit
+  __shared__ double s_sum[NW][32];
+  __shared__ float s_max[NW][32];
+  __shared__ float s_min[NW][32];
   const int b = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int m = blockIdx.x * 32 + lane;
@@ -63,7 +64,22 @@ __global__ void colstats_kernel(const T* __restrict__ x, int K, int64_t x_sb, in
   double sum = 0.0;
   float mx = -INFINITY, mn = INFINITY;
   if (live) {
-    for (int k = warp; k < K; k += 8) {
+    // eight rows per trip: a warp has that many loads in flight instead of one (the walk is bound by latency, not by
+    // bytes)
+    constexpr int U = 8;
+    int k = warp;
+    for (; k + NW * (U - 1) < K; k += NW * U) {
+      float v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) v[u] = to_f32(xb[(int64_t)(k + NW * u) * x_sk]);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        sum += (double)v[u];
+        mx = fmaxf(mx, v[u]);
+        mn = fminf(mn, v[u]);
+      }
+    }
+    for (; k < K; k += NW) {
       const float v = to_f32(xb[(int64_t)k * x_sk]);
       sum += (double)v;
       mx = fmaxf(mx, v);
@@ -75,7 +91,7 @@ __global__ void colstats_kernel(const T* __restrict__ x, int K, int64_t x_sb, in
   s_min[warp][lane] = mn;
   __syncthreads();
   if (warp == 0 && live) {
-    for (int w = 1; w < 8; ++w) {
+    for (int w = 1; w < NW; ++w) {
       sum += s_sum[w][lane];
       mx = fmaxf(mx, s_max[w][lane]);
       mn = fminf(mn, s_min[w][lane]);
@@ -139,9 +155,9 @@ extern "C" int fa_colstats(const void* x, int dtype, int B, int K, int64_t x_sb,
   dim3 grid(ceil_div(Mc, 32), B);
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == FA_DTYPE_F16)
-    colstats_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, K, x_sb, x_sk, idx, Mc, avg, dev);
+    colstats_kernel<__half><<<grid, 1024, 0, st>>>((const __half*)x, K, x_sb, x_sk, idx, Mc, avg, dev);
   else
-    colstats_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, K, x_sb, x_sk, idx, Mc, avg, dev);
+    colstats_kernel<__nv_bfloat16><<<grid, 1024, 0, st>>>((const __nv_bfloat16*)x, K, x_sb, x_sk, idx, Mc, avg, dev);
   FA_CHECK_LAUNCH("fa_colstats");
   return FA_OK;
 }
